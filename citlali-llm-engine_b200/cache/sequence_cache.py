@@ -32,10 +32,12 @@ PAGE_SIZE = 64
 @dataclass(frozen=True)
 class KVRequirement:
     """What an attention-like mixer needs cached per token: keys and values of ``num_kv_heads``
-    heads of ``head_dim``; ``window`` keys back at most (None: all of them)."""
+    heads of ``head_dim``; ``window`` keys back at most (None: all of them).  ``value_dim``: the size of a value
+    (None: ``head_dim``; 0: the mixer keeps one vector per token and no values, and the group holds no value pool)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -113,11 +115,12 @@ class SequenceCache:
         self._has_window = any(req.window is not None for req in by_kv)
         for req, steps in by_kv.items():
             shape = (len(steps), self.num_pages, req.num_kv_heads, page_size, req.head_dim)
+            value_dim = req.head_dim if req.value_dim is None else req.value_dim
             table_host = torch.zeros((num_slots, self.max_pages_per_slot), dtype=torch.int32)
             group = KVGroup(req, steps, PageAllocator(self.num_pages), table_host,
                             torch.zeros_like(table_host, device=self.device),
                             torch.zeros(shape, dtype=dtype, device=self.device),
-                            torch.zeros(shape, dtype=dtype, device=self.device))
+                            torch.zeros(shape[:-1] + (value_dim,), dtype=dtype, device=self.device))
             for j, s in enumerate(steps):
                 self._where[s] = ("kv", len(self.kv_groups), j)
             self.kv_groups.append(group)
@@ -227,7 +230,7 @@ class SequenceCache:
     def bytes(self) -> int:
         total = 0
         for g in self.kv_groups:
-            total += 2 * g.keys.numel() * g.keys.element_size()
+            total += (g.keys.numel() + g.values.numel()) * g.keys.element_size()
         for g in self.state_groups:
             total += g.storage.numel() * g.storage.element_size()
         return total

@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (config.json ``architectures[0]``) to the
+"""One registry from an architecture's name (config.json ``architectures[0]``, or ``architecture``) to the
 class that reads its configuration and describes its model.
 
 The reference only checks that the GGUF architecture string contains "qwen"
@@ -35,11 +35,18 @@ def config_class_for(name: str):
     return _ARCHITECTURES[name]
 
 
-def config_from_dict(d: Dict[str, Any]):
+def architecture_name(d: Dict[str, Any]) -> str:
+    """``architectures[0]``, or, in a config.json that has no such list, the string ``architecture``."""
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        return d["architecture"]
     require(isinstance(archs, list) and len(archs) >= 1 and isinstance(archs[0], str),
-            "config.json: 'architectures' must be a non-empty list of names")
-    return config_class_for(archs[0]).from_dict(d)
+            "config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name)")
+    return archs[0]
+
+
+def config_from_dict(d: Dict[str, Any]):
+    return config_class_for(architecture_name(d)).from_dict(d)
 
 
 def config_from_model_dir(model_dir: str):

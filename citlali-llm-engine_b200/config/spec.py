@@ -63,6 +63,9 @@ class ModelSpec:
     stop_token_ids: Tuple[int, ...] = ()
     embedding_scale: Optional[float] = None  # the embedding rows are multiplied by it (None: a plain row copy)
     logit_scale: Optional[float] = None      # the logits are multiplied by it (None: as the output matrix gives them)
+    # None: one residual stream [rows, hidden].  A number S: the residual is S streams [S, rows, hidden] that all start
+    # as the embedding's rows and are summed before the last norm; every layer's block must be one that takes streams.
+    residual_streams: Optional[int] = None
 
     def validate(self):
         from ..errors import require

@@ -149,6 +149,59 @@ int citlali_gemm_tc_set_pair_rows(int rows);
 int citlali_wait_selftest(int32_t* error_flag, int* result, long long limit_ns, cudaStream_t stream);
 int citlali_gemm_tc_runs_on_pairs(int M, int N, int K, int sm_count, int gate_runs);
 
+// ---- residual streams (hyper-connections) ----------------------------------------------------------------------
+// X [streams, rows, width] float32, `stream_stride` elements between streams.
+// out[r, :] = u / sqrt(mean(u^2) + eps) * gain with u = sum_s w_in[s] X[s, r, :]; gain float32 [width].
+int citlali_hyper_read_norm(const float* X, size_t stream_stride, int streams, const float* w_in, const float* gain,
+                            void* out, int out_dtype, int rows, int width, float eps, cudaStream_t stream);
+// X[t, e] <- sum_s w_mix[s * streams + t] X[s, e] + w_out[t] y[e] for the n elements of a stream, all t from the old values.
+int citlali_hyper_write(float* X, size_t stream_stride, int streams, const float* y, const float* w_mix,
+                        const float* w_out, size_t n, cudaStream_t stream);
+// out[i, :] = sum_s X[s, index[i], :]  (index may be null: identity).
+int citlali_stream_sum(const float* X, size_t stream_stride, int streams, const int32_t* index, float* out, int rows,
+                       int width, cudaStream_t stream);
+// y = max(x, 0)^2 over n elements.
+int citlali_relu_squared(const void* x, void* y, int dtype, size_t n, cudaStream_t stream);
+
+// ---- the gated delta rule --------------------------------------------------------------------------------------
+// proj [rows, proj_stride] float32 = q (KH D) | k (KH D) | v (H V) | gate (H V) | b (H) | a (H) per row.  Convolves the
+// q, k, v channels over time (taps_w [C, taps], the last column is the current token's; earlier tokens come from the
+// step's rows or from state[slot][conv_off ...], laid out [taps - 1, C]), applies SiLU, makes q and k heads unit
+// vectors (q also times D^-1/2), and writes prep [rows, C + 2 H] = q | k | v | sigmoid(b) | exp(-exp(a_log) softplus(a +
+// dt_bias)).  Then stores each sequence's last taps - 1 inputs in its state.
+int citlali_delta_prepare(const float* proj, int proj_stride, const float* taps_w, int taps, float* state,
+                          size_t state_stride, size_t conv_off, const int32_t* row_slot, const int32_t* seq_start,
+                          const int32_t* seq_slot, int sequences, const float* a_log, const float* dt_bias, float* prep,
+                          int rows, int H, int KH, int D, int V, float unit_eps, cudaStream_t stream);
+// The recurrence over each sequence's rows, from and into state[slot][0 ...] = S [H, D, V]; out [rows, H V] float32.
+int citlali_delta_rule(const float* prep, int prep_stride, float* state, size_t state_stride, const int32_t* seq_start,
+                       const int32_t* seq_slot, int sequences, int H, int KH, int D, int V, float* out,
+                       cudaStream_t stream);
+// y[r, h, :] = o[r, h, :] / sqrt(mean(o^2) + eps) * weight * silu(gate[r * gate_stride + h V ...]).
+int citlali_delta_output(const float* o, const float* gate, int gate_stride, const float* weight, void* y, int y_dtype,
+                         int rows, int H, int V, float eps, cudaStream_t stream);
+
+// ---- attention through a shared latent -------------------------------------------------------------------------
+// proj [rows, proj_stride] float32 = query latent (RQ) | latent (R) | shared key part (P) | ...; cq [rows, RQ] receives
+// the normed query latent; with has_kv the normed latent and the key part, rotated by the row's position in pairs
+// (2i, 2i+1) below rot_dims, go to pool [page, page_size, R + P] at the row's slot and position.
+int citlali_latent_prepare(const float* proj, int proj_stride, int RQ, int R, int P, int has_kv, const float* q_weight,
+                           const float* c_weight, const float* inv_freq, int rot_dims, const int32_t* row_slot,
+                           const int32_t* row_pos, const int32_t* page_table, int table_stride, void* pool,
+                           int cache_dtype, int page_size, void* cq, int cq_dtype, int rows, float eps, cudaStream_t stream);
+// y[r, h, n] = sum_k x[r * x_row + h * x_head + k] M[h * m_head + k * m_k + n * m_n]; with tail > 0 the elements
+// x[r, h, K .. K + tail) are rotated like a key part and copied to y[r, h, N ...]; with gate, y *= sigmoid(gate[r, h N + n]).
+int citlali_heads_product(const void* x, int x_dtype, size_t x_row, int x_head, const void* M, int m_dtype, size_t m_head,
+                          int m_k, int m_n, void* y, int y_dtype, size_t y_row, int y_head, int rows, int heads, int K,
+                          int N, int tail, const float* inv_freq, int rot_dims, const int32_t* row_pos, const float* gate,
+                          size_t gate_stride, cudaStream_t stream);
+// out[r, h, :R] = sum_j p_j c_j over the keys lo..pos of the row's slot (lo = 0, or pos - window + 1 with a window),
+// p = softmax of scale * q[r, h, :] . pool[j, :], the denominator also counting exp(sink[h]) when sink is given.
+int citlali_latent_attention(const float* q, const void* pool, int cache_dtype, const int32_t* page_table,
+                             int table_stride, const int32_t* row_slot, const int32_t* row_pos, const float* sink,
+                             float* out, int rows, int H, int R, int E, int page_size, int window, float scale,
+                             cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

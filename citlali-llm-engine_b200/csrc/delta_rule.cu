@@ -1,0 +1,258 @@
+// The gated delta rule: a recurrent mixer whose state per head is a matrix S [D, V] in float32.
+//
+// For every token, with unit vectors q and k (q also times D^-1/2), a value v, a write strength beta in (0, 1) and a
+// decay g in (0, 1):   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q.
+// The columns of S do not meet: column j only ever needs v[j], so a thread owns one column in registers and walks its
+// sequence's tokens in order.  One order of operations serves prompts, parts of prompts and single tokens, so the
+// state and the outputs do not depend on how a sequence was cut into steps.
+//
+// Three kernels:
+//   delta_prepare   one block a row: the short causal convolution over time of the q, k, v channels (earlier tokens
+//                   from the step's rows or, before its first row, from the sequence's kept inputs), SiLU, unit length
+//                   for q and k heads, beta = sigmoid(.), g = exp(-exp(A_log) softplus(. + dt_bias)).  All float32.
+//                   A second launch then moves the sequence's last taps-1 inputs into its state.
+//   delta_rule      one warp a (sequence, head, 32 columns): the recurrence.
+//   delta_output    one block a row: each head's output divided by its root mean square, times a weight, times
+//                   SiLU(gate); rounded once to the compute dtype.
+#include "api.h"
+#include "common.cuh"
+
+namespace citlali {
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float siluf_(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+
+// proj [rows, proj_stride] float32 holds, per row: q (KH*D) | k (KH*D) | v (H*V) | gate (H*V) | b (H) | a (H).
+// prep [rows, C + 2H] receives q^ | k^ | v | beta | g, C = 2 KH D + H V.
+// conv_state [slot] is [taps-1, C]: the inputs at the sequence's last taps-1 positions, oldest first.
+__global__ void __launch_bounds__(256)
+delta_prepare_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ taps_w, int taps,
+                     const float* __restrict__ state, size_t state_stride, size_t conv_off,
+                     const int32_t* __restrict__ row_slot, const float* __restrict__ a_log,
+                     const float* __restrict__ dt_bias, float* __restrict__ prep, int H, int KH, int D, int V, float unit_eps) {
+    extern __shared__ float act[];          // C floats
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.x;
+    const int C = 2 * KH * D + H * V;
+    const int slot = row_slot[row];
+    int in_step = 0;                        // how many of the tokens before this one are rows of this step
+    while (in_step < taps - 1 && row - in_step - 1 >= 0 && row_slot[row - in_step - 1] == slot) ++in_step;
+    const float* kept = state + (size_t)slot * state_stride + conv_off;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = taps - 1; j >= 0; --j) {                 // j tokens back; oldest first
+            float x;
+            if (j <= in_step) x = proj[(size_t)(row - j) * proj_stride + c];
+            else x = kept[(size_t)(taps - 1 - j + in_step) * C + c];
+            acc = fmaf(taps_w[(size_t)c * taps + (taps - 1 - j)], x, acc);
+        }
+        act[c] = siluf_(acc);
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int head = warp; head < 2 * KH; head += warps) {     // q heads, then k heads
+        float* v = act + head * D;
+        float ss = 0.0f;
+        for (int i = lane; i < D; i += 32) ss = fmaf(v[i], v[i], ss);
+        ss = warp_sum(ss);
+        float f = rsqrtf(ss + unit_eps);
+        if (head < KH) f *= rsqrtf((float)D);
+        for (int i = lane; i < D; i += 32) v[i] *= f;
+    }
+    __syncthreads();
+    float* dst = prep + (size_t)row * (C + 2 * H);
+    for (int c = threadIdx.x; c < C; c += blockDim.x) dst[c] = act[c];
+    const float* rest = proj + (size_t)row * proj_stride + C + H * V;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        dst[C + h] = sigmoidf_(rest[h]);
+        dst[C + H + h] = expf(-expf(a_log[h]) * softplusf_(rest[H + h] + dt_bias[h]));
+    }
+}
+
+// After the step's rows were convolved: the sequence keeps its last taps-1 inputs.  One thread a channel.
+__global__ void delta_conv_state_kernel(const float* __restrict__ proj, int proj_stride, int taps, float* __restrict__ state,
+                                        size_t state_stride, size_t conv_off, const int32_t* __restrict__ seq_start,
+                                        const int32_t* __restrict__ seq_slot, int C) {
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int seq = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int r0 = seq_start[seq], n = seq_start[seq + 1] - r0, keep = taps - 1;
+    float* kept = state + (size_t)seq_slot[seq] * state_stride + conv_off;
+    if (n >= keep) {
+        for (int i = 0; i < keep; ++i) kept[(size_t)i * C + c] = proj[(size_t)(r0 + n - keep + i) * proj_stride + c];
+    } else {
+        for (int i = 0; i < keep - n; ++i) kept[(size_t)i * C + c] = kept[(size_t)(i + n) * C + c];
+        for (int i = 0; i < n; ++i) kept[(size_t)(keep - n + i) * C + c] = proj[(size_t)(r0 + i) * proj_stride + c];
+    }
+}
+
+// One warp a (sequence, head, 32 columns of S).  DP: the head size rounded up to a multiple of 32; rows of S beyond D
+// stay zero.  The next token's q, k, v, beta, g are fetched into registers while the current token is computed.
+template <int DP>
+__global__ void __launch_bounds__(128)
+delta_rule_kernel(const float* __restrict__ prep, int prep_stride, float* __restrict__ state, size_t state_stride,
+                  const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot, int sequences,
+                  int H, int KH, int D, int V, float* __restrict__ out) {
+    __shared__ __align__(16) float kq[4][2 * DP];
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int chunks = (V + 31) / 32;
+    const long unit = (long)blockIdx.x * 4 + warp;
+    if (unit >= (long)sequences * H * chunks) return;
+    const int chunk = (int)(unit % chunks);
+    const int head = (int)((unit / chunks) % H);
+    const int seq = (int)(unit / ((long)chunks * H));
+    const int col = chunk * 32 + lane;
+    const bool live = col < V;
+    const int kv_head = head / (H / KH);
+    const int C = 2 * KH * D + H * V;
+    const int r0 = seq_start[seq], r1 = seq_start[seq + 1];
+    float* S_g = state + (size_t)seq_slot[seq] * state_stride + (size_t)head * D * V + col;
+    float S[DP];
+#pragma unroll
+    for (int i = 0; i < DP; ++i) S[i] = (live && i < D) ? S_g[(size_t)i * V] : 0.0f;
+    float* ks = kq[warp];
+    float* qs = kq[warp] + DP;
+    constexpr int PER = DP / 32;
+    float k_next[PER], q_next[PER], v_next = 0.0f, beta_next = 0.0f, g_next = 0.0f;
+    auto fetch = [&](int row) {
+        const float* p = prep + (size_t)row * prep_stride;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int i = j * 32 + lane;
+            q_next[j] = i < D ? p[kv_head * D + i] : 0.0f;
+            k_next[j] = i < D ? p[(KH + kv_head) * D + i] : 0.0f;
+        }
+        v_next = live ? p[2 * KH * D + head * V + col] : 0.0f;
+        beta_next = p[C + head];
+        g_next = p[C + H + head];
+    };
+    if (r0 < r1) fetch(r0);
+    for (int row = r0; row < r1; ++row) {
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            ks[j * 32 + lane] = k_next[j];
+            qs[j * 32 + lane] = q_next[j];
+        }
+        const float v = v_next, beta = beta_next, g = g_next;
+        __syncwarp();
+        if (row + 1 < r1) fetch(row + 1);
+        float sk = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DP; i += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
+            sk = fmaf(S[i], k4.x, sk); sk = fmaf(S[i + 1], k4.y, sk);
+            sk = fmaf(S[i + 2], k4.z, sk); sk = fmaf(S[i + 3], k4.w, sk);
+        }
+        const float u = beta * (v - g * sk);
+        float o = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DP; i += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
+            const float4 q4 = *reinterpret_cast<const float4*>(qs + i);
+            S[i] = fmaf(k4.x, u, g * S[i]);         o = fmaf(S[i], q4.x, o);
+            S[i + 1] = fmaf(k4.y, u, g * S[i + 1]); o = fmaf(S[i + 1], q4.y, o);
+            S[i + 2] = fmaf(k4.z, u, g * S[i + 2]); o = fmaf(S[i + 2], q4.z, o);
+            S[i + 3] = fmaf(k4.w, u, g * S[i + 3]); o = fmaf(S[i + 3], q4.w, o);
+        }
+        if (live) out[(size_t)row * H * V + head * V + col] = o;
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DP; ++i)
+            if (i < D) S_g[(size_t)i * V] = S[i];
+    }
+}
+
+// y[row, h, :] = o[row, h, :] / sqrt(mean(o^2) + eps) * weight * silu(gate[row, h, :]).  One warp a head.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+delta_output_kernel(const float* __restrict__ o, const float* __restrict__ gate, int gate_stride,
+                    const float* __restrict__ weight, TO* __restrict__ y, int H, int V, float eps) {
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int h = warp; h < H; h += warps) {
+        const float* src = o + ((size_t)row * H + h) * V;
+        float ss = 0.0f;
+        for (int i = lane; i < V; i += 32) ss = fmaf(src[i], src[i], ss);
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)V + eps);
+        const float* gt = gate + (size_t)row * gate_stride + h * V;
+        for (int i = lane; i < V; i += 32)
+            stf(y, ((size_t)row * H + h) * V + i, src[i] * inv * weight[i] * siluf_(gt[i]));
+    }
+}
+
+}  // namespace citlali
+
+using namespace citlali;
+
+extern "C" int citlali_delta_prepare(const float* proj, int proj_stride, const float* taps_w, int taps, float* state,
+                                     size_t state_stride, size_t conv_off, const int32_t* row_slot,
+                                     const int32_t* seq_start, const int32_t* seq_slot, int sequences,
+                                     const float* a_log, const float* dt_bias, float* prep, int rows, int H, int KH,
+                                     int D, int V, float unit_eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (H <= 0 || KH <= 0 || H % KH != 0 || D <= 0 || V <= 0 || taps < 1) {
+        set_last_error("delta_prepare: %d heads over %d key heads of %d, values of %d, %d taps", H, KH, D, V, taps);
+        return kBadShape;
+    }
+    const int C = 2 * KH * D + H * V;
+    const size_t smem = (size_t)C * sizeof(float);
+    if (smem > 200 * 1024) {
+        set_last_error("delta_prepare: %d convolved channels do not fit in shared memory", C);
+        return kTooLarge;
+    }
+    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_kernel(delta_prepare_kernel, rows, 256, smem, stream, proj, proj_stride, taps_w, taps, (const float*)state,
+                  state_stride, conv_off, row_slot, a_log, dt_bias, prep, H, KH, D, V, unit_eps);
+    int code = CITLALI_LAUNCH_CHECK();
+    if (code != 0 || taps == 1) return code;
+    dim3 grid(sequences, (C + 127) / 128);
+    launch_kernel(delta_conv_state_kernel, grid, 128, 0, stream, proj, proj_stride, taps, state, state_stride, conv_off,
+                  seq_start, seq_slot, C);
+    return CITLALI_LAUNCH_CHECK();
+}
+
+extern "C" int citlali_delta_rule(const float* prep, int prep_stride, float* state, size_t state_stride,
+                                  const int32_t* seq_start, const int32_t* seq_slot, int sequences, int H, int KH, int D,
+                                  int V, float* out, cudaStream_t stream) {
+    if (sequences <= 0) return 0;
+    if (D > 256) {
+        set_last_error("delta_rule: a head size of %d exceeds 256", D);
+        return kTooLarge;
+    }
+    const long units = (long)sequences * H * ((V + 31) / 32);
+    const int blocks = (int)((units + 3) / 4);
+#define CITLALI_DELTA(DP)                                                                                         \
+    launch_kernel(delta_rule_kernel<DP>, blocks, 128, 0, stream, prep, prep_stride, state, state_stride, seq_start, \
+                  seq_slot, sequences, H, KH, D, V, out)
+    switch ((D + 31) / 32) {
+        case 1: CITLALI_DELTA(32); break;
+        case 2: CITLALI_DELTA(64); break;
+        case 3: CITLALI_DELTA(96); break;
+        case 4: CITLALI_DELTA(128); break;
+        case 5: CITLALI_DELTA(160); break;
+        case 6: CITLALI_DELTA(192); break;
+        case 7: CITLALI_DELTA(224); break;
+        default: CITLALI_DELTA(256); break;
+    }
+#undef CITLALI_DELTA
+    return CITLALI_LAUNCH_CHECK();
+}
+
+extern "C" int citlali_delta_output(const float* o, const float* gate, int gate_stride, const float* weight, void* y,
+                                    int y_dtype, int rows, int H, int V, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    return CITLALI_DISPATCH_FLOAT(y_dtype, TO, [&] {
+        launch_kernel(delta_output_kernel<TO>, rows, 256, 0, stream, o, gate, gate_stride, weight, (TO*)y, H, V, eps);
+        return CITLALI_LAUNCH_CHECK();
+    });
+}

@@ -1,0 +1,126 @@
+// Hyper-connections: the residual is kept as S parallel streams X [S, rows, W] in float32.  A sub-layer reads one
+// mixture of them, u = sum_s in[s] X_s, and its output y goes back into all of them at once,
+// X_t <- sum_s mix[s, t] X_s + out[t] y.  With S = 1, in = out = mix = 1 this is the plain residual sum.
+//
+//   hyper_read_norm   one block a row: u, then u / sqrt(mean(u^2) + eps) * gain, rounded once to the compute dtype.
+//   hyper_write       one thread an element of a row: the S old values are read, the S new ones written in place.
+//   stream_sum        out[i] = sum_s X[s, index[i]]: what the model's last norm reads.
+// Also here: the squared ReLU of a feed-forward without a gate.
+#include "api.h"
+#include "common.cuh"
+
+namespace citlali {
+
+constexpr int kMaxStreams = 8;
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+hyper_read_norm_kernel(const float* __restrict__ X, size_t stream_stride, int S, const float* __restrict__ w_in,
+                       const float* __restrict__ gain, TO* __restrict__ out, int W, float eps) {
+    extern __shared__ float u[];
+    __shared__ float scratch[32];
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.x;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float v = 0.0f;
+        for (int s = 0; s < S; ++s) v = fmaf(w_in[s], X[s * stream_stride + (size_t)row * W + i], v);
+        u[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) stf(out, (size_t)row * W + i, u[i] * inv * gain[i]);
+}
+
+__global__ void hyper_write_kernel(float* __restrict__ X, size_t stream_stride, int S, const float* __restrict__ y,
+                                   const float* __restrict__ w_mix, const float* __restrict__ w_out, size_t n) {
+    dependents_may_launch();
+    wait_for_predecessor();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        float old[kMaxStreams];
+        for (int s = 0; s < S; ++s) old[s] = X[s * stream_stride + e];
+        const float yv = y[e];
+        for (int t = 0; t < S; ++t) {
+            float v = 0.0f;
+            for (int s = 0; s < S; ++s) v = fmaf(w_mix[s * S + t], old[s], v);
+            X[t * stream_stride + e] = fmaf(w_out[t], yv, v);
+        }
+    }
+}
+
+__global__ void stream_sum_kernel(const float* __restrict__ X, size_t stream_stride, int S,
+                                  const int32_t* __restrict__ index, float* __restrict__ out, int W) {
+    dependents_may_launch();
+    wait_for_predecessor();
+    const size_t src = (size_t)(index ? index[blockIdx.x] : blockIdx.x) * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float v = 0.0f;
+        for (int s = 0; s < S; ++s) v += X[s * stream_stride + src + i];
+        out[(size_t)blockIdx.x * W + i] = v;
+    }
+}
+
+template <typename T>
+__global__ void relu_squared_kernel(const T* x, T* y, size_t n) {
+    dependents_may_launch();
+    wait_for_predecessor();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const float v = fmaxf(ldf(x, e), 0.0f);
+        stf(y, e, v * v);
+    }
+}
+
+static int grid_for(size_t n) {
+    const size_t blocks = (n + 255) / 256;
+    return (int)(blocks < 8192 ? blocks : 8192);
+}
+
+}  // namespace citlali
+
+using namespace citlali;
+
+extern "C" int citlali_hyper_read_norm(const float* X, size_t stream_stride, int streams, const float* w_in,
+                                       const float* gain, void* out, int out_dtype, int rows, int width, float eps,
+                                       cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (streams < 1 || smem > 200 * 1024) {
+        set_last_error("hyper_read_norm: %d streams of width %d", streams, width);
+        return kBadShape;
+    }
+    return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(hyper_read_norm_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_kernel(hyper_read_norm_kernel<TO>, rows, 256, smem, stream, X, stream_stride, streams, w_in, gain, (TO*)out,
+                      width, eps);
+        return CITLALI_LAUNCH_CHECK();
+    });
+}
+
+extern "C" int citlali_hyper_write(float* X, size_t stream_stride, int streams, const float* y, const float* w_mix,
+                                   const float* w_out, size_t n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    if (streams < 1 || streams > kMaxStreams) {
+        set_last_error("hyper_write: %d streams (1 to %d are taken)", streams, kMaxStreams);
+        return kBadShape;
+    }
+    launch_kernel(hyper_write_kernel, grid_for(n), 256, 0, stream, X, stream_stride, streams, y, w_mix, w_out, n);
+    return CITLALI_LAUNCH_CHECK();
+}
+
+extern "C" int citlali_stream_sum(const float* X, size_t stream_stride, int streams, const int32_t* index, float* out,
+                                  int rows, int width, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    launch_kernel(stream_sum_kernel, rows, 256, 0, stream, X, stream_stride, streams, index, out, width);
+    return CITLALI_LAUNCH_CHECK();
+}
+
+extern "C" int citlali_relu_squared(const void* x, void* y, int dtype, size_t n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    return CITLALI_DISPATCH_FLOAT(dtype, T, [&] {
+        launch_kernel(relu_squared_kernel<T>, grid_for(n), 256, 0, stream, (const T*)x, (T*)y, n);
+        return CITLALI_LAUNCH_CHECK();
+    });
+}

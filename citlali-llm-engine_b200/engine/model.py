@@ -64,6 +64,11 @@ class DecoderModel:
         self.head = DenseLinear([spec.head_name], [spec.vocab_size], spec.hidden_size)
         self.embedding: Optional[torch.Tensor] = None
         self.tied = None
+        streams = spec.residual_streams
+        for i, block in enumerate(self.layers):
+            takes = getattr(block, "residual_streams", None)
+            require(takes == streams, f"layer {i}'s block works on {takes or 'one'} residual stream(s), the model has "
+                                      f"{streams or 'one'}")
 
     def tensor_specs(self) -> List[TensorSpec]:
         return expected_tensors(self.spec)
@@ -105,9 +110,15 @@ class DecoderModel:
     def forward(self, batch: StepBatch, cache) -> torch.Tensor:
         """Logits ``[wanted, vocab]`` float32 for ``batch.want_rows``, in that order."""
         ctx, spec = self.ctx, self.spec
-        x = torch.empty((batch.rows, spec.hidden_size), dtype=torch.float32, device=ctx.device)
-        ops.embed_rows(self.embedding, batch.tokens, x, ctx.error_flag,
-                       1.0 if spec.embedding_scale is None else float(spec.embedding_scale))
+        streams = spec.residual_streams
+        emb_scale = 1.0 if spec.embedding_scale is None else float(spec.embedding_scale)
+        if streams is None:
+            x = torch.empty((batch.rows, spec.hidden_size), dtype=torch.float32, device=ctx.device)
+            ops.embed_rows(self.embedding, batch.tokens, x, ctx.error_flag, emb_scale)
+        else:                       # every stream starts as the embedding's rows
+            x = torch.empty((streams, batch.rows, spec.hidden_size), dtype=torch.float32, device=ctx.device)
+            for s in range(streams):
+                ops.embed_rows(self.embedding, batch.tokens, x[s], ctx.error_flag, emb_scale)
         batch.norm_carry = None
         for i, step in enumerate(spec.schedule):
             source = i if step.cache_of is None else step.cache_of
@@ -119,7 +130,12 @@ class DecoderModel:
         wanted = int(batch.want_rows.numel())
         if wanted == 0:
             return torch.empty((0, spec.vocab_size), dtype=torch.float32, device=ctx.device)
-        h = self.final_norm.forward(x, row_index=batch.want_rows)
+        if streams is None:
+            h = self.final_norm.forward(x, row_index=batch.want_rows)
+        else:
+            summed = torch.empty((wanted, spec.hidden_size), dtype=torch.float32, device=ctx.device)
+            ops.stream_sum(x, summed, batch.want_rows)
+            h = self.final_norm.forward(summed)
         logits = self.head.forward(h, out_dtype=torch.float32)
         if spec.logit_scale is not None:
             ops.scale_(logits, float(spec.logit_scale))

@@ -432,3 +432,130 @@ def gemm_tc(x, w, y, accumulate=False, error_flag=None, swiglu=False, force_spli
                                         _i(force_splits), _ptr(error_flag), _i(sm_count(x.device)), _ptr(emit_rows),
                                         _ptr(emit_sumsq), _ptr(scale_sumsq), _i(groups), _i(int(dim)), _f(float(eps)), _stream()),
            "gemm_tc")
+
+
+# ---- residual streams --------------------------------------------------------------------------
+
+_sz = ctypes.c_size_t
+
+
+def hyper_read_norm(X: torch.Tensor, w_in: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor):
+    """``out = rms_norm(sum_s w_in[s] X[s]) * gain``; X float32 [streams, rows, width], gain float32."""
+    _need_cuda(X, w_in, gain, out)
+    S, rows, width = X.shape
+    require(X.dtype == torch.float32 and w_in.dtype == torch.float32 and gain.dtype == torch.float32
+            and w_in.numel() == S and gain.numel() == width and out.shape == (rows, width),
+            "hyper_read_norm: shapes or dtypes do not fit")
+    _check(lib().citlali_hyper_read_norm(_ptr(X), _sz(rows * width), _i(S), _ptr(w_in), _ptr(gain), _ptr(out),
+                                         _i(_dtype_code(out)), _i(rows), _i(width), _f(eps), _stream()), "hyper_read_norm")
+
+
+def hyper_write(X: torch.Tensor, y: torch.Tensor, w_mix: torch.Tensor, w_out: torch.Tensor):
+    """``X[t] <- sum_s w_mix[s, t] X[s] + w_out[t] y`` in place, every stream from the old ones."""
+    _need_cuda(X, y, w_mix, w_out)
+    S, rows, width = X.shape
+    require(X.dtype == torch.float32 and y.dtype == torch.float32 and y.shape == (rows, width)
+            and w_mix.dtype == torch.float32 and w_mix.shape == (S, S) and w_out.dtype == torch.float32
+            and w_out.numel() == S, "hyper_write: shapes or dtypes do not fit")
+    _check(lib().citlali_hyper_write(_ptr(X), _sz(rows * width), _i(S), _ptr(y), _ptr(w_mix), _ptr(w_out),
+                                     _sz(rows * width), _stream()), "hyper_write")
+
+
+def stream_sum(X: torch.Tensor, out: torch.Tensor, row_index: Optional[torch.Tensor] = None):
+    """``out[i] = sum_s X[s, row_index[i]]``."""
+    _need_cuda(X, out, row_index)
+    S, rows, width = X.shape
+    require(X.dtype == torch.float32 and out.dtype == torch.float32 and out.shape[1] == width
+            and (row_index is None or (row_index.dtype == torch.int32 and row_index.numel() == out.shape[0])),
+            "stream_sum: shapes or dtypes do not fit")
+    _check(lib().citlali_stream_sum(_ptr(X), _sz(rows * width), _i(S), _ptr(row_index), _ptr(out), _i(out.shape[0]),
+                                    _i(width), _stream()), "stream_sum")
+
+
+def relu_squared(x: torch.Tensor, y: torch.Tensor):
+    _need_cuda(x, y)
+    require(x.dtype == y.dtype and x.shape == y.shape, "relu_squared: shapes or dtypes do not fit")
+    _check(lib().citlali_relu_squared(_ptr(x), _ptr(y), _i(_dtype_code(x)), _sz(x.numel()), _stream()), "relu_squared")
+
+
+# ---- the gated delta rule ------------------------------------------------------------------------
+
+def delta_prepare(proj, taps_w, state, conv_off, row_slot, seq_start, seq_slot, sequences, a_log, dt_bias, prep,
+                  H, KH, D, V, unit_eps):
+    """See ``citlali_delta_prepare`` (csrc/api.h).  ``state`` [slots, n] float32; two launches unless taps == 1."""
+    _need_cuda(proj, taps_w, state, row_slot, seq_start, seq_slot, a_log, dt_bias, prep)
+    rows = proj.shape[0]
+    C = 2 * KH * D + H * V
+    taps = taps_w.shape[1]
+    require(proj.dtype == torch.float32 and prep.dtype == torch.float32 and state.dtype == torch.float32
+            and taps_w.dtype == torch.float32 and a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32,
+            "delta_prepare: float32 tensors only")
+    require(proj.shape[1] >= C + H * V + 2 * H and prep.shape == (rows, C + 2 * H) and taps_w.shape[0] == C
+            and state.dim() == 2 and state.shape[1] >= conv_off + (taps - 1) * C, "delta_prepare: shapes do not fit")
+    _check(lib().citlali_delta_prepare(_ptr(proj), _i(proj.shape[1]), _ptr(taps_w), _i(taps), _ptr(state),
+                                       _sz(state.shape[1]), _sz(conv_off), _ptr(row_slot), _ptr(seq_start), _ptr(seq_slot),
+                                       _i(sequences), _ptr(a_log), _ptr(dt_bias), _ptr(prep), _i(rows), _i(H), _i(KH),
+                                       _i(D), _i(V), _f(unit_eps), _stream()), "delta_prepare" if taps == 1 else "delta_prepare_kept")
+
+
+_KERNELS_PER_CALL["delta_prepare_kept"] = 2
+
+
+def delta_rule(prep, state, seq_start, seq_slot, sequences, H, KH, D, V, out):
+    _need_cuda(prep, state, seq_start, seq_slot, out)
+    require(prep.dtype == torch.float32 and state.dtype == torch.float32 and out.dtype == torch.float32
+            and out.shape == (prep.shape[0], H * V) and state.shape[1] >= H * D * V, "delta_rule: shapes or dtypes do not fit")
+    _check(lib().citlali_delta_rule(_ptr(prep), _i(prep.shape[1]), _ptr(state), _sz(state.shape[1]), _ptr(seq_start),
+                                    _ptr(seq_slot), _i(sequences), _i(H), _i(KH), _i(D), _i(V), _ptr(out), _stream()),
+           "delta_rule")
+
+
+def delta_output(o, gate, gate_stride, weight, y, H, V, eps):
+    """``gate``: a view into the projection's rows that starts at the gate's first column."""
+    _need_cuda(o, weight, y)
+    require(gate.is_cuda and o.dtype == torch.float32 and gate.dtype == torch.float32 and weight.dtype == torch.float32
+            and weight.numel() == V and y.shape == o.shape, "delta_output: shapes or dtypes do not fit")
+    _check(lib().citlali_delta_output(_ptr(o), _ptr(gate), _i(gate_stride), _ptr(weight), _ptr(y), _i(_dtype_code(y)),
+                                      _i(o.shape[0]), _i(H), _i(V), _f(eps), _stream()), "delta_output")
+
+
+# ---- attention through a shared latent -------------------------------------------------------------
+
+def latent_prepare(proj, RQ, R, P, has_kv, q_weight, c_weight, inv_freq, rot_dims, row_slot, row_pos, page_table, pool,
+                   page_size, cq, eps):
+    _need_cuda(proj, q_weight, c_weight, inv_freq, row_slot, row_pos, page_table, pool, cq)
+    rows = proj.shape[0]
+    require(proj.dtype == torch.float32 and q_weight.dtype == torch.float32 and cq.shape == (rows, RQ)
+            and proj.shape[1] >= RQ + (R + P if has_kv else 0), "latent_prepare: shapes or dtypes do not fit")
+    if has_kv:
+        require(pool is not None and pool.shape[-1] == R + P and c_weight.dtype == torch.float32
+                and (rot_dims == 0 or (inv_freq is not None and inv_freq.numel() == rot_dims // 2)),
+                "latent_prepare: the cache or the rotation's table does not fit")
+    _check(lib().citlali_latent_prepare(
+        _ptr(proj), _i(proj.shape[1]), _i(RQ), _i(R), _i(P), _i(1 if has_kv else 0), _ptr(q_weight), _ptr(c_weight),
+        _ptr(inv_freq), _i(rot_dims), _ptr(row_slot), _ptr(row_pos), _ptr(page_table), _i(page_table.shape[1]), _ptr(pool),
+        _i(_dtype_code(pool) if pool is not None else _F32), _i(page_size), _ptr(cq), _i(_dtype_code(cq)), _i(rows),
+        _f(eps), _stream()), "latent_prepare")
+
+
+def heads_product(x, x_row, x_head, M, m_head, m_k, m_n, y, y_row, y_head, rows, heads, K, N, tail=0, inv_freq=None,
+                  rot_dims=0, row_pos=None, gate=None, gate_stride=0):
+    """``y[r, h, :N] = x[r, h, :K] . M_h`` with a matrix per head given by strides; see ``citlali_heads_product``."""
+    _need_cuda(M, y, inv_freq, row_pos)
+    require(x.is_cuda and (gate is None or (gate.is_cuda and gate.dtype == torch.float32)), "heads_product: bad operands")
+    _check(lib().citlali_heads_product(
+        _ptr(x), _i(_dtype_code(x)), _sz(x_row), _i(x_head), _ptr(M), _i(_dtype_code(M)), _sz(m_head), _i(m_k), _i(m_n),
+        _ptr(y), _i(_dtype_code(y)), _sz(y_row), _i(y_head), _i(rows), _i(heads), _i(K), _i(N), _i(tail), _ptr(inv_freq),
+        _i(rot_dims), _ptr(row_pos), _ptr(gate), _sz(gate_stride), _stream()), "heads_product")
+
+
+def latent_attention(q, pool, page_table, row_slot, row_pos, sink, out, H, R, E, page_size, window, scale):
+    _need_cuda(q, pool, page_table, row_slot, row_pos, sink, out)
+    rows = q.shape[0]
+    require(q.dtype == torch.float32 and out.dtype == torch.float32 and q.shape == (rows, H * E)
+            and out.shape == (rows, H * R) and pool.shape[-1] == E and (sink is None or (sink.dtype == torch.float32
+            and sink.numel() == H)), "latent_attention: shapes or dtypes do not fit")
+    _check(lib().citlali_latent_attention(_ptr(q), _ptr(pool), _i(_dtype_code(pool)), _ptr(page_table),
+                                          _i(page_table.shape[1]), _ptr(row_slot), _ptr(row_pos), _ptr(sink), _ptr(out),
+                                          _i(rows), _i(H), _i(R), _i(E), _i(page_size), _i(int(window or 0)), _f(scale),
+                                          _stream()), "latent_attention")

@@ -56,4 +56,36 @@ class GatedSiluFeedForward:
         return residual
 
 
+class SquaredReluFeedForward:
+    """y = W_down max(W_up h, 0)^2, no gate.  Parameters: hidden_size, intermediate_size; optional ``up`` and ``down``
+    (the matrices' full names; default ``<prefix>.up_proj.weight`` and ``<prefix>.down_proj.weight``)."""
+    graph_safe = True
+    can_overwrite = True
+
+    def __init__(self, params, prefix: str):
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.up = DenseLinear([str(params.get("up") or f"{prefix}.up_proj.weight")], [self.inter], self.hidden)
+        self.down = DenseLinear([str(params.get("down") or f"{prefix}.down_proj.weight")], [self.hidden], self.inter)
+
+    def tensor_specs(self):
+        return self.up.tensor_specs() + self.down.tensor_specs()
+
+    def bind(self, weights, ctx):
+        self.up.bind(weights, ctx)
+        self.down.bind(weights, ctx)
+        self.dtype = ctx.dtype
+
+    def forward(self, h, batch, residual, overwrite=False):
+        """``overwrite``: ``residual`` holds nothing yet and receives the output instead of being added to."""
+        z = self.up.forward(h)
+        ops.relu_squared(z, z)
+        if overwrite:
+            self.down.forward(z, out=residual)
+        else:
+            self.down.forward(z, accumulate_into=residual)
+        return residual
+
+
 register_part("feed_forward", "gated_silu", GatedSiluFeedForward)
+register_part("feed_forward", "relu_squared", SquaredReluFeedForward)

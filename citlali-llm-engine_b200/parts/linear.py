@@ -106,14 +106,18 @@ class DenseLinear:
         return act
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-                accumulate_into: Optional[torch.Tensor] = None, row_scale=None, emit=None) -> torch.Tensor:
+                accumulate_into: Optional[torch.Tensor] = None, row_scale=None, emit=None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``accumulate_into`` (float32 [rows, out]) receives ``+= x . W^T`` and is returned;
-        otherwise a new tensor of ``out_dtype`` (default: the compute dtype).  Few rows, tensor-core shapes only:
+        otherwise ``out`` if given, else a new tensor of ``out_dtype`` (default: the compute dtype).  Few rows, tensor-core shapes only:
         ``row_scale`` (``NormedRows.scale`` of the rows ``x`` stands for) scales the result rows; ``emit`` (a pair of
         buffers, with ``accumulate_into``) receives the updated rows as bfloat16 and their sums of squares."""
         rows = x.shape[0]
         if accumulate_into is not None:
             y = accumulate_into
+        elif out is not None:                    # a buffer the caller owns receives the product
+            require(out.shape == (rows, self.out_features), "the output buffer has the wrong shape")
+            y = out
         else:
             y = torch.empty((rows, self.out_features), dtype=out_dtype or self.dtype, device=x.device)
         if rows == 0:

@@ -1,7 +1,11 @@
 """RMSNorm over the hidden size: y = x * rsqrt(mean(x^2) + eps) * gain, eps inside the root,
 the gain multiplies (no 1 + gain) -- rms_norm_kernel, src/compute/cuda/kernels.cu:73-92.
 Input is the float32 residual stream; the sum of squares, the root and the product are
-32-bit, rounded once at the store to the compute dtype."""
+32-bit, rounded once at the store to the compute dtype.
+
+Parameters: size, eps; optional ``tensor`` (the gain's full name; default ``<prefix>.weight``) and ``offset``
+(the factor is ``offset + w``: a gain stored around zero has offset 1; the sum is made once, in 32-bit, and the gain
+then stays 32-bit in both paths, since 1 + w rounded to bfloat16 would lose most of w)."""
 from __future__ import annotations
 
 import torch
@@ -17,7 +21,8 @@ class RMSNorm:
     def __init__(self, params, prefix: str):
         self.size = int(params["size"])
         self.eps = float(params["eps"])
-        self.name = f"{prefix}.weight"
+        self.name = str(params.get("tensor") or f"{prefix}.weight")
+        self.offset = float(params.get("offset", 0.0))
         self.gain = None
         self.gain_downstream = False
 
@@ -26,6 +31,8 @@ class RMSNorm:
 
     def bind(self, weights, ctx):
         self.gain = bind_gain(weights, self.name, self.size, ctx)
+        if self.offset != 0.0:
+            self.gain = (self.gain.to(torch.float32) + self.offset).contiguous()
         self.dtype = ctx.dtype
 
     def gain_moves_downstream(self) -> torch.Tensor:

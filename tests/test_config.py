@@ -65,8 +65,8 @@ def test_required_keys(key):
         cb.config_from_dict(d)
 
 
-def test_registry_names_one_architecture_and_lists_it_on_a_miss():
-    assert cb.registered_architectures() == ["Qwen3ForCausalLM"]
+def test_registry_names_its_architectures_and_lists_them_on_a_miss():
+    assert cb.registered_architectures() == ["Lanizen", "Qwen3ForCausalLM"]
     with pytest.raises(cb.CitlaliError, match="unknown architecture 'LlamaForCausalLM'.*Qwen3ForCausalLM"):
         cb.config_from_dict(dict(TINY["A"], architectures=["LlamaForCausalLM"]))
     with pytest.raises(cb.CitlaliError, match="architectures"):
