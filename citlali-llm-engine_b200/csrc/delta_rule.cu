@@ -57,8 +57,8 @@ delta_prepare_kernel(const float* __restrict__ proj, int proj_stride, const floa
         float ss = 0.0f;
         for (int i = lane; i < D; i += 32) ss = fmaf(v[i], v[i], ss);
         ss = warp_sum(ss);
-        float f = rsqrtf(ss + unit_eps);
-        if (head < KH) f *= rsqrtf((float)D);
+        float f = 1.0f / sqrtf(ss + unit_eps);
+        if (head < KH) f /= sqrtf((float)D);
         for (int i = lane; i < D; i += 32) v[i] *= f;
     }
     __syncthreads();
@@ -183,7 +183,7 @@ delta_output_kernel(const float* __restrict__ o, const float* __restrict__ gate,
         float ss = 0.0f;
         for (int i = lane; i < V; i += 32) ss = fmaf(src[i], src[i], ss);
         ss = warp_sum(ss);
-        const float inv = rsqrtf(ss / (float)V + eps);
+        const float inv = 1.0f / sqrtf(ss / (float)V + eps);
         const float* gt = gate + (size_t)row * gate_stride + h * V;
         for (int i = lane; i < V; i += 32)
             stf(y, ((size_t)row * H + h) * V + i, src[i] * inv * weight[i] * siluf_(gt[i]));

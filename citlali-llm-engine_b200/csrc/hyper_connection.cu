@@ -30,7 +30,7 @@ hyper_read_norm_kernel(const float* __restrict__ X, size_t stream_stride, int S,
         ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, scratch);
-    const float inv = rsqrtf(ss / (float)W + eps);
+    const float inv = 1.0f / sqrtf(ss / (float)W + eps);
     for (int i = threadIdx.x; i < W; i += blockDim.x) stf(out, (size_t)row * W + i, u[i] * inv * gain[i]);
 }
 

@@ -33,14 +33,14 @@ latent_prepare_kernel(const float* __restrict__ proj, int proj_stride, int RQ, i
     float ss = 0.0f;
     for (int i = threadIdx.x; i < RQ; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
     ss = block_sum(ss, scratch);
-    float inv = rsqrtf(ss / (float)RQ + eps);
+    float inv = 1.0f / sqrtf(ss / (float)RQ + eps);
     for (int i = threadIdx.x; i < RQ; i += blockDim.x) stf(cq, (size_t)row * RQ + i, src[i] * inv * q_weight[i]);
     if (!has_kv) return;
     const float* c = src + RQ;
     ss = 0.0f;
     for (int i = threadIdx.x; i < R; i += blockDim.x) ss = fmaf(c[i], c[i], ss);
     ss = block_sum(ss, scratch);
-    inv = rsqrtf(ss / (float)R + eps);
+    inv = 1.0f / sqrtf(ss / (float)R + eps);
     const int pos = row_pos[row];
     const int page = page_table[(size_t)row_slot[row] * table_stride + pos / page_size];
     TC* dst = pool + ((size_t)page * page_size + pos % page_size) * (R + P);
