@@ -201,6 +201,12 @@ int citlali_latent_attention(const float* q, const void* pool, int cache_dtype, 
                              int table_stride, const int32_t* row_slot, const int32_t* row_pos, const float* sink,
                              float* out, int rows, int H, int R, int E, int page_size, int window, float scale,
                              cudaStream_t stream);
+// The same walk on the tensor cores for a bfloat16 cache (sixteen heads of a token are an MMA tile's rows); E a multiple
+// of 16, R a multiple of 64 (citlali_latent_attention_mma_supports).
+int citlali_latent_attention_mma_supports(int R, int E);
+int citlali_latent_attention_mma(const float* q, const void* pool, const int32_t* page_table, int table_stride,
+                                 const int32_t* row_slot, const int32_t* row_pos, const float* sink, float* out, int rows,
+                                 int H, int R, int E, int page_size, int window, float scale, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -2,8 +2,8 @@
 //
 // For every token, with unit vectors q and k (q also times D^-1/2), a value v, a write strength beta in (0, 1) and a
 // decay g in (0, 1):   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q.
-// The columns of S do not meet: column j only ever needs v[j], so a thread owns one column in registers and walks its
-// sequence's tokens in order.  One order of operations serves prompts, parts of prompts and single tokens, so the
+// The columns of S do not meet: column j only ever needs v[j], so four lanes own one column in registers and walk
+// their sequence's tokens in order.  One order of operations serves prompts, parts of prompts and single tokens, so the
 // state and the outputs do not depend on how a sequence was cut into steps.
 //
 // Three kernels:
@@ -11,7 +11,7 @@
 //                   from the step's rows or, before its first row, from the sequence's kept inputs), SiLU, unit length
 //                   for q and k heads, beta = sigmoid(.), g = exp(-exp(A_log) softplus(. + dt_bias)).  All float32.
 //                   A second launch then moves the sequence's last taps-1 inputs into its state.
-//   delta_rule      one warp a (sequence, head, 32 columns): the recurrence.
+//   delta_rule      one warp a (sequence, head, 8 columns), four lanes a column: the recurrence.
 //   delta_output    one block a row: each head's output divided by its root mean square, times a weight, times
 //                   SiLU(gate); rounded once to the compute dtype.
 #include "api.h"
@@ -22,6 +22,9 @@ namespace citlali {
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float siluf_(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
 
 // proj [rows, proj_stride] float32 holds, per row: q (KH*D) | k (KH*D) | v (H*V) | gate (H*V) | b (H) | a (H).
 // prep [rows, C + 2H] receives q^ | k^ | v | beta | g, C = 2 KH D + H V.
@@ -90,83 +93,109 @@ __global__ void delta_conv_state_kernel(const float* __restrict__ proj, int proj
     }
 }
 
-// One warp a (sequence, head, 32 columns of S).  DP: the head size rounded up to a multiple of 32; rows of S beyond D
-// stay zero.  The next token's q, k, v, beta, g are fetched into registers while the current token is computed.
+// One warp a (sequence, head, 8 columns of S); four lanes share a column and hold a quarter of its rows each (the
+// 16-byte groups of rows g with g mod 4 = the lane's part, so that the four parts read neighbouring words of shared
+// memory).  DP: the head size rounded up to a multiple of 32; rows of S beyond D stay zero.  The two dot products of a
+// token are summed over a lane's rows first and over the four lanes after, in one fixed order.  The inputs of the next
+// tokens (seven, or three for heads over 128) are on their way into a ring in shared memory (cp.async) while the current token is computed.
 template <int DP>
 __global__ void __launch_bounds__(128)
 delta_rule_kernel(const float* __restrict__ prep, int prep_stride, float* __restrict__ state, size_t state_stride,
                   const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot, int sequences,
                   int H, int KH, int D, int V, float* __restrict__ out) {
-    __shared__ __align__(16) float kq[4][2 * DP];
+    constexpr int STAGES = DP <= 128 ? 8 : 4;    // tokens in flight from global memory: a warp is alone with their latency
+    constexpr int STRIDE = 2 * DP + 16;          // floats a token takes in the ring: k | q | v of 8 columns | beta | g
+    __shared__ __align__(16) float ring[4][STAGES][STRIDE];
     dependents_may_launch();
     wait_for_predecessor();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int chunks = (V + 31) / 32;
+    const int part = lane & 3;
+    const int chunks = (V + 7) / 8;
     const long unit = (long)blockIdx.x * 4 + warp;
     if (unit >= (long)sequences * H * chunks) return;
     const int chunk = (int)(unit % chunks);
     const int head = (int)((unit / chunks) % H);
     const int seq = (int)(unit / ((long)chunks * H));
-    const int col = chunk * 32 + lane;
+    const int col = chunk * 8 + (lane >> 2);
     const bool live = col < V;
     const int kv_head = head / (H / KH);
     const int C = 2 * KH * D + H * V;
     const int r0 = seq_start[seq], r1 = seq_start[seq + 1];
     float* S_g = state + (size_t)seq_slot[seq] * state_stride + (size_t)head * D * V + col;
-    float S[DP];
+    constexpr int GROUPS = DP / 16;              // 16-byte groups of rows a lane holds
+    float S[GROUPS][4];
 #pragma unroll
-    for (int i = 0; i < DP; ++i) S[i] = (live && i < D) ? S_g[(size_t)i * V] : 0.0f;
-    float* ks = kq[warp];
-    float* qs = kq[warp] + DP;
+    for (int j = 0; j < GROUPS; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = (4 * j + part) * 4 + e;
+            S[j][e] = (live && i < D) ? S_g[(size_t)i * V] : 0.0f;
+        }
     constexpr int PER = DP / 32;
-    float k_next[PER], q_next[PER], v_next = 0.0f, beta_next = 0.0f, g_next = 0.0f;
-    auto fetch = [&](int row) {
-        const float* p = prep + (size_t)row * prep_stride;
+    for (int i = lane; i < STAGES * STRIDE; i += 32) (&ring[warp][0][0])[i] = 0.0f;     // rows beyond D and dead columns stay zero
+    __syncwarp();
+    auto issue = [&](int row) {                  // the row's inputs into its place in the ring, asynchronously
+        if (row < r1) {
+            const float* p = prep + (size_t)row * prep_stride;
+            float* dst = ring[warp][(row - r0) % STAGES];
 #pragma unroll
-        for (int j = 0; j < PER; ++j) {
-            const int i = j * 32 + lane;
-            q_next[j] = i < D ? p[kv_head * D + i] : 0.0f;
-            k_next[j] = i < D ? p[(KH + kv_head) * D + i] : 0.0f;
+            for (int j = 0; j < PER; ++j) {
+                const int i = j * 32 + lane;
+                if (i < D) {
+                    cp_async4(dst + i, p + (KH + kv_head) * D + i);
+                    cp_async4(dst + DP + i, p + kv_head * D + i);
+                }
+            }
+            if (lane < 8 && chunk * 8 + lane < V) cp_async4(dst + 2 * DP + lane, p + 2 * KH * D + head * V + chunk * 8 + lane);
+            if (lane == 8) cp_async4(dst + 2 * DP + 8, p + C + head);
+            if (lane == 9) cp_async4(dst + 2 * DP + 9, p + C + H + head);
         }
-        v_next = live ? p[2 * KH * D + head * V + col] : 0.0f;
-        beta_next = p[C + head];
-        g_next = p[C + H + head];
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    if (r0 < r1) fetch(r0);
+    for (int s = 0; s < STAGES - 1; ++s) issue(r0 + s);
     for (int row = r0; row < r1; ++row) {
-        __syncwarp();
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+        __syncwarp();                            // this row's inputs are visible; the row before is no longer read
+        issue(row + STAGES - 1);
+        const float* cur = ring[warp][(row - r0) % STAGES];
+        const float* ks = cur;
+        const float* qs = cur + DP;
+        const float v = cur[2 * DP + (lane >> 2)], beta = cur[2 * DP + 8], g = cur[2 * DP + 9];
+        float sk0 = 0.0f, sk1 = 0.0f;
 #pragma unroll
-        for (int j = 0; j < PER; ++j) {
-            ks[j * 32 + lane] = k_next[j];
-            qs[j * 32 + lane] = q_next[j];
+        for (int j = 0; j < GROUPS; ++j) {
+            const float4 k4 = *reinterpret_cast<const float4*>(ks + (4 * j + part) * 4);
+            sk0 = fmaf(S[j][0], k4.x, sk0); sk1 = fmaf(S[j][1], k4.y, sk1);
+            sk0 = fmaf(S[j][2], k4.z, sk0); sk1 = fmaf(S[j][3], k4.w, sk1);
         }
-        const float v = v_next, beta = beta_next, g = g_next;
-        __syncwarp();
-        if (row + 1 < r1) fetch(row + 1);
-        float sk = 0.0f;
-#pragma unroll
-        for (int i = 0; i < DP; i += 4) {
-            const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
-            sk = fmaf(S[i], k4.x, sk); sk = fmaf(S[i + 1], k4.y, sk);
-            sk = fmaf(S[i + 2], k4.z, sk); sk = fmaf(S[i + 3], k4.w, sk);
-        }
+        float sk = sk0 + sk1;
+        sk += __shfl_xor_sync(0xffffffffu, sk, 1);
+        sk += __shfl_xor_sync(0xffffffffu, sk, 2);
         const float u = beta * (v - g * sk);
-        float o = 0.0f;
+        float o0 = 0.0f, o1 = 0.0f;
 #pragma unroll
-        for (int i = 0; i < DP; i += 4) {
-            const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
-            const float4 q4 = *reinterpret_cast<const float4*>(qs + i);
-            S[i] = fmaf(k4.x, u, g * S[i]);         o = fmaf(S[i], q4.x, o);
-            S[i + 1] = fmaf(k4.y, u, g * S[i + 1]); o = fmaf(S[i + 1], q4.y, o);
-            S[i + 2] = fmaf(k4.z, u, g * S[i + 2]); o = fmaf(S[i + 2], q4.z, o);
-            S[i + 3] = fmaf(k4.w, u, g * S[i + 3]); o = fmaf(S[i + 3], q4.w, o);
+        for (int j = 0; j < GROUPS; ++j) {
+            const float4 k4 = *reinterpret_cast<const float4*>(ks + (4 * j + part) * 4);
+            const float4 q4 = *reinterpret_cast<const float4*>(qs + (4 * j + part) * 4);
+            S[j][0] = fmaf(k4.x, u, g * S[j][0]); o0 = fmaf(S[j][0], q4.x, o0);
+            S[j][1] = fmaf(k4.y, u, g * S[j][1]); o1 = fmaf(S[j][1], q4.y, o1);
+            S[j][2] = fmaf(k4.z, u, g * S[j][2]); o0 = fmaf(S[j][2], q4.z, o0);
+            S[j][3] = fmaf(k4.w, u, g * S[j][3]); o1 = fmaf(S[j][3], q4.w, o1);
         }
-        if (live) out[(size_t)row * H * V + head * V + col] = o;
+        float o = o0 + o1;
+        o += __shfl_xor_sync(0xffffffffu, o, 1);
+        o += __shfl_xor_sync(0xffffffffu, o, 2);
+        if (live && part == 0) out[(size_t)row * H * V + head * V + col] = o;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (live) {
 #pragma unroll
-        for (int i = 0; i < DP; ++i)
-            if (i < D) S_g[(size_t)i * V] = S[i];
+        for (int j = 0; j < GROUPS; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = (4 * j + part) * 4 + e;
+                if (i < D) S_g[(size_t)i * V] = S[j][e];
+            }
     }
 }
 
@@ -229,7 +258,7 @@ extern "C" int citlali_delta_rule(const float* prep, int prep_stride, float* sta
         set_last_error("delta_rule: a head size of %d exceeds 256", D);
         return kTooLarge;
     }
-    const long units = (long)sequences * H * ((V + 31) / 32);
+    const long units = (long)sequences * H * ((V + 7) / 8);
     const int blocks = (int)((units + 3) / 4);
 #define CITLALI_DELTA(DP)                                                                                         \
     launch_kernel(delta_rule_kernel<DP>, blocks, 128, 0, stream, prep, prep_stride, state, state_stride, seq_start, \

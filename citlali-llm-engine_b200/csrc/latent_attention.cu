@@ -14,6 +14,7 @@
 //                      softmax in float32 whose denominator also counts exp(sink) once.
 #include "api.h"
 #include "common.cuh"
+#include "mma_common.cuh"
 
 namespace citlali {
 
@@ -58,6 +59,33 @@ latent_prepare_kernel(const float* __restrict__ proj, int proj_stride, int RQ, i
         stf(dst, R + 2 * i + 1, b);
     }
     if ((P & 1) && threadIdx.x == 0) stf(dst, R + P - 1, r[P - 1]);
+}
+
+// x[row, h, K .. K + tail) rotated by the row's position (pairs (2i, 2i+1) below rot_dims) and written to
+// y[row, h, N .. N + tail), for `count` rows from row0 on; the block's threads share the work.
+template <typename TX, typename TY>
+__device__ __forceinline__ void rotate_tail(const TX* __restrict__ x, size_t x_row, int x_head, TY* __restrict__ y, size_t y_row,
+                                            int y_head, int h, int row0, int count, int rows, int K, int N, int tail,
+                                            const float* __restrict__ inv_freq, int rot_dims,
+                                            const int32_t* __restrict__ row_pos) {
+    const int pairs = (tail + 1) / 2;
+    for (int e = threadIdx.x; e < count * pairs; e += blockDim.x) {
+        const int r = e / pairs, i = e % pairs, row = row0 + r;
+        if (row >= rows) continue;
+        const TX* src = x + (size_t)row * x_row + (size_t)h * x_head + K;
+        TY* dst = y + (size_t)row * y_row + (size_t)h * y_head + N;
+        float a = ldf(src, 2 * i);
+        if (2 * i + 1 >= tail) { stf(dst, 2 * i, a); continue; }
+        float b = ldf(src, 2 * i + 1);
+        if (2 * i + 1 < rot_dims) {
+            float sn, cs;
+            sincosf((float)row_pos[row] * inv_freq[i], &sn, &cs);
+            const float a2 = a * cs - b * sn, b2 = b * cs + a * sn;
+            a = a2; b = b2;
+        }
+        stf(dst, 2 * i, a);
+        stf(dst, 2 * i + 1, b);
+    }
 }
 
 // y[row, h, n] = sum_k x[row * x_row + h * x_head + k] * M[h * m_head + k * m_k + n * m_n],  n < N, k < K.
@@ -107,25 +135,68 @@ heads_product_kernel(const TX* __restrict__ x, size_t x_row, int x_head, const T
             stf(y, (size_t)row * y_row + (size_t)h * y_head + n, v);
         }
     }
-    if (tail > 0 && blockIdx.z == 0) {
-        for (int e = threadIdx.x; e < 8 * ((tail + 1) / 2); e += 256) {
-            const int r = e / ((tail + 1) / 2), i = e % ((tail + 1) / 2), row = row0 + r;
-            if (row >= rows) continue;
-            const TX* src = x + (size_t)row * x_row + (size_t)h * x_head + K;
-            TY* dst = y + (size_t)row * y_row + (size_t)h * y_head + N;
-            float a = ldf(src, 2 * i);
-            if (2 * i + 1 >= tail) { stf(dst, 2 * i, a); continue; }
-            float b = ldf(src, 2 * i + 1);
-            if (2 * i + 1 < rot_dims) {
-                float sn, cs;
-                sincosf((float)row_pos[row] * inv_freq[i], &sn, &cs);
-                const float a2 = a * cs - b * sn, b2 = b * cs + a * sn;
-                a = a2; b = b2;
-            }
-            stf(dst, 2 * i, a);
-            stf(dst, 2 * i + 1, b);
+    if (tail > 0 && blockIdx.z == 0)
+        rotate_tail(x, x_row, x_head, y, y_row, y_head, h, row0, 8, rows, K, N, tail, inv_freq, rot_dims, row_pos);
+}
+
+// The same product on the tensor cores for bfloat16 matrices: a block of four warps computes 64 rows x 64 columns of one
+// head (a warp: 16 rows), x and M_h pass through shared memory as bfloat16 in tiles of 32 k (M_h laid [n][k] whatever
+// its strides), m16n8k16 MMAs with float accumulators, k ascending.
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(128)
+heads_product_mma_kernel(const TX* __restrict__ x, size_t x_row, int x_head, const __nv_bfloat16* __restrict__ M,
+                         size_t m_head, int m_k, int m_n, TY* __restrict__ y, size_t y_row, int y_head, int rows, int K,
+                         int N, int tail, const float* __restrict__ inv_freq, int rot_dims,
+                         const int32_t* __restrict__ row_pos, const float* __restrict__ gate, size_t gate_stride) {
+    __shared__ __align__(16) __nv_bfloat16 xs[64][40];
+    __shared__ __align__(16) __nv_bfloat16 ms[64][40];
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int h = blockIdx.y, row0 = blockIdx.x * 64, n0 = blockIdx.z * 64;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    float acc[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+    const uint32_t xs_a = (uint32_t)__cvta_generic_to_shared(&xs[0][0]), ms_a = (uint32_t)__cvta_generic_to_shared(&ms[0][0]);
+    for (int k0 = 0; k0 < K; k0 += 32) {
+        for (int e = threadIdx.x; e < 64 * 32; e += 128) {
+            const int r = e >> 5, k = e & 31;
+            xs[r][k] = __float2bfloat16_rn((row0 + r < rows && k0 + k < K)
+                                           ? ldf(x, (size_t)(row0 + r) * x_row + (size_t)h * x_head + k0 + k) : 0.0f);
         }
+        for (int e = threadIdx.x; e < 64 * 32; e += 128) {
+            const int k = m_n == 1 ? e >> 6 : e & 31, n = m_n == 1 ? e & 63 : e >> 5;     // the matrix's contiguous axis first
+            ms[n][k] = (k0 + k < K && n0 + n < N) ? M[(size_t)h * m_head + (size_t)(k0 + k) * m_k + (size_t)(n0 + n) * m_n]
+                                                  : __float2bfloat16_rn(0.0f);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 32; kk += 16) {
+            uint32_t a0, a1, a2, a3;
+            fa::ldmatrix_x4(xs_a + (uint32_t)(((warp * 16 + (lane & 15)) * 40 + kk + (lane >> 4) * 8) * 2), a0, a1, a2, a3);
+#pragma unroll
+            for (int n = 0; n < 8; n += 2) {
+                uint32_t b0, b1, b2, b3;
+                fa::ldmatrix_x4(ms_a + (uint32_t)(((n * 8 + ((lane >> 4) << 3) + (lane & 7)) * 40 + kk + ((lane >> 3) & 1) * 8) * 2),
+                                b0, b1, b2, b3);
+                fa::mma_16816(acc[n], a0, a1, a2, a3, b0, b1);
+                fa::mma_16816(acc[n + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+        __syncthreads();
     }
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int row = row0 + warp * 16 + g + (c >> 1) * 8, col = n0 + n * 8 + t * 2 + (c & 1);
+            if (row >= rows || col >= N) continue;
+            float v = acc[n][c];
+            if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)row * gate_stride + (size_t)h * N + col]));
+            stf(y, (size_t)row * y_row + (size_t)h * y_head + col, v);
+        }
+    if (tail > 0 && blockIdx.z == 0)
+        rotate_tail(x, x_row, x_head, y, y_row, y_head, h, row0, 64, rows, K, N, tail, inv_freq, rot_dims, row_pos);
 }
 
 // q [rows, H, E] float32 (E = R + P: the query in the latent's coordinates, then its rotated part); the cache's pool
@@ -222,6 +293,17 @@ extern "C" int citlali_heads_product(const void* x, int x_dtype, size_t x_row, i
     if (tail > 0 && (rot_dims > tail || (rot_dims & 1) || (rot_dims > 0 && (!inv_freq || !row_pos)))) {
         set_last_error("heads_product: %d rotated dimensions of a tail of %d", rot_dims, tail);
         return kBadShape;
+    }
+    if (m_dtype == kBF16 && rows >= 16) {                    // enough rows to fill MMA tiles
+        dim3 grid((rows + 63) / 64, heads, (N + 63) / 64);
+        return CITLALI_DISPATCH_FLOAT(x_dtype, TX, [&] {
+            return CITLALI_DISPATCH_FLOAT(y_dtype, TY, [&] {
+                launch_kernel(heads_product_mma_kernel<TX, TY>, grid, 128, 0, stream, (const TX*)x, x_row, x_head,
+                              (const __nv_bfloat16*)M, m_head, m_k, m_n, (TY*)y, y_row, y_head, rows, K, N, tail, inv_freq,
+                              rot_dims, row_pos, gate, gate_stride);
+                return CITLALI_LAUNCH_CHECK();
+            });
+        });
     }
     dim3 grid((rows + 7) / 8, heads, (N + 63) / 64);
     return CITLALI_DISPATCH_FLOAT(x_dtype, TX, [&] {

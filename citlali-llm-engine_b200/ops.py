@@ -549,12 +549,23 @@ def heads_product(x, x_row, x_head, M, m_head, m_k, m_n, y, y_row, y_head, rows,
         _i(rot_dims), _ptr(row_pos), _ptr(gate), _sz(gate_stride), _stream()), "heads_product")
 
 
-def latent_attention(q, pool, page_table, row_slot, row_pos, sink, out, H, R, E, page_size, window, scale):
+def latent_attention(q, pool, page_table, row_slot, row_pos, sink, out, H, R, E, page_size, window, scale,
+                     tensor_cores=None):
+    """The walk over a latent cache.  A bfloat16 cache whose sizes the tensor-core kernel takes runs that kernel
+    (``tensor_cores`` False: never), everything else the one on CUDA cores, which is exact in 32-bit."""
     _need_cuda(q, pool, page_table, row_slot, row_pos, sink, out)
     rows = q.shape[0]
     require(q.dtype == torch.float32 and out.dtype == torch.float32 and q.shape == (rows, H * E)
             and out.shape == (rows, H * R) and pool.shape[-1] == E and (sink is None or (sink.dtype == torch.float32
             and sink.numel() == H)), "latent_attention: shapes or dtypes do not fit")
+    if (tensor_cores is not False and pool.dtype == torch.bfloat16
+            and lib().citlali_latent_attention_mma_supports(_i(R), _i(E))):
+        _check(lib().citlali_latent_attention_mma(_ptr(q), _ptr(pool), _ptr(page_table), _i(page_table.shape[1]),
+                                                  _ptr(row_slot), _ptr(row_pos), _ptr(sink), _ptr(out), _i(rows), _i(H),
+                                                  _i(R), _i(E), _i(page_size), _i(int(window or 0)), _f(scale), _stream()),
+               "latent_attention_mma")
+        return
+    require(tensor_cores is not True, "latent_attention: the tensor-core kernel does not take this cache")
     _check(lib().citlali_latent_attention(_ptr(q), _ptr(pool), _i(_dtype_code(pool)), _ptr(page_table),
                                           _i(page_table.shape[1]), _ptr(row_slot), _ptr(row_pos), _ptr(sink), _ptr(out),
                                           _i(rows), _i(H), _i(R), _i(E), _i(page_size), _i(int(window or 0)), _f(scale),

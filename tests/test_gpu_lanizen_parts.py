@@ -367,3 +367,49 @@ def test_heads_product_both_orientations(dtype):
                       gate=gd[:, 5:], gate_stride=gd.shape[1])
     want = torch.einsum("rhk,hnk->rhn", x2.view(rows, H, K).double(), Mt.view(H, N, K).double()).reshape(rows, H * N)
     close(out, want * torch.sigmoid(gate[:, 5:].double()), dtype, bf16=1e-2)
+
+
+# ---- the walk on the tensor cores (bfloat16 caches whose sizes it takes) -------------------------------------------
+
+@pytest.mark.parametrize("H, R, E, T", [(5, 64, 80, 200), (20, 128, 192, 150), (16, 512, 576, 130), (33, 192, 208, 70)])
+def test_walk_on_tensor_cores_against_plain(H, R, E, T):
+    keys = (0.5 * torch.randn(T, E)).to(torch.bfloat16).float()
+    positions = [T - 1, 0, 63, 64, 65, T // 2]
+    q = torch.randn(len(positions), H * E).to(torch.bfloat16).float()
+    sink = torch.randn(H)
+    order = torch.randperm((T + 63) // 64).tolist()
+    for window in (0, 70):
+        for sk in (None, sink):
+            got = _latent_walk(q, keys, order, positions, sk, H, R, E, window, 0.1, dtype=torch.bfloat16)
+            close(got, _walk_plain(q, keys, positions, sk, H, R, E, window, 0.1), torch.bfloat16, bf16=1e-2)
+
+
+@pytest.mark.parametrize("window", [1, 2, 63, 64, 65, 130])
+def test_tensor_core_walk_window_edges_and_far_key(window):
+    H, R, E, T = 3, 64, 80, 460
+    keys = (0.1 * torch.randn(T, E)).to(torch.bfloat16).float()
+    q = torch.zeros(2, H * E)
+    q[:, R] = 1.0                                              # head 0 asks for the marked direction
+    for marked in (0, 63, 64, 200):
+        ks = keys.clone()
+        ks[marked, R] = 60.0
+        positions = [marked + window - 1, marked + window]
+        got = _latent_walk(q, ks, list(range(8))[::-1], positions, None, H, R, E, window, 1.0, dtype=torch.bfloat16)
+        close(got, _walk_plain(q, ks, positions, None, H, R, E, window, 1.0), torch.bfloat16, bf16=1e-2)
+        assert torch.allclose(got[0, :R], ks[marked, :R], atol=1e-3)
+        assert not torch.allclose(got[1, :R], ks[marked, :R], atol=1e-2)
+    # without a window the first key still reaches the last row
+    ks = keys.clone()
+    ks[0, R] = 60.0
+    got = _latent_walk(q[:1], ks, list(range(8)), [T - 1], None, H, R, E, 0, 1.0, dtype=torch.bfloat16)
+    assert torch.allclose(got[0, :R], ks[0, :R], atol=1e-3)
+
+
+def test_tensor_core_walk_does_not_depend_on_the_batch():
+    """A row's result is the same bits alone and among other rows, in any order, whatever pages it lies in."""
+    H, R, E, T = 8, 64, 80, 300
+    keys = torch.randn(T, E).to(torch.bfloat16).float()
+    q = torch.randn(4, H * E)
+    a = _latent_walk(q, keys, list(range(5)), [299, 10, 150, 64], None, H, R, E, 100, 0.2, dtype=torch.bfloat16)
+    b = _latent_walk(q[[2, 0]], keys, [4, 2, 0, 1, 3], [150, 299], None, H, R, E, 100, 0.2, dtype=torch.bfloat16)
+    assert torch.equal(a[2], b[0]) and torch.equal(a[0], b[1])
