@@ -157,6 +157,10 @@ int citlali_hyper_read_norm(const float* X, size_t stream_stride, int streams, c
 // X[t, e] <- sum_s w_mix[s * streams + t] X[s, e] + w_out[t] y[e] for the n elements of a stream, all t from the old values.
 int citlali_hyper_write(float* X, size_t stream_stride, int streams, const float* y, const float* w_mix,
                         const float* w_out, size_t n, cudaStream_t stream);
+// citlali_hyper_write, then citlali_hyper_read_norm of the new values with w_in and gain, in one pass over the streams.
+int citlali_hyper_write_read_norm(float* X, size_t stream_stride, int streams, const float* y, const float* w_mix,
+                                  const float* w_out, const float* w_in, const float* gain, void* out, int out_dtype,
+                                  int rows, int width, float eps, cudaStream_t stream);
 // out[i, :] = sum_s X[s, index[i], :]  (index may be null: identity).
 int citlali_stream_sum(const float* X, size_t stream_stride, int streams, const int32_t* index, float* out, int rows,
                        int width, cudaStream_t stream);
@@ -202,11 +206,13 @@ int citlali_latent_attention(const float* q, const void* pool, int cache_dtype, 
                              float* out, int rows, int H, int R, int E, int page_size, int window, float scale,
                              cudaStream_t stream);
 // The same walk on the tensor cores for a bfloat16 cache (sixteen heads of a token are an MMA tile's rows); E a multiple
-// of 16, R a multiple of 64 (citlali_latent_attention_mma_supports).
+// of 16, R a multiple of 64 (citlali_latent_attention_mma_supports).  splits > 1: a (row, sixteen heads) unit's key tiles
+// are dealt to that many blocks and merged by a second kernel; partial holds units * splits * 16 * (R + 2) floats.
 int citlali_latent_attention_mma_supports(int R, int E);
 int citlali_latent_attention_mma(const float* q, const void* pool, const int32_t* page_table, int table_stride,
                                  const int32_t* row_slot, const int32_t* row_pos, const float* sink, float* out, int rows,
-                                 int H, int R, int E, int page_size, int window, float scale, cudaStream_t stream);
+                                 int H, int R, int E, int page_size, int window, float scale, int splits, float* partial,
+                                 size_t partial_floats, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -95,7 +95,7 @@ __global__ void delta_conv_state_kernel(const float* __restrict__ proj, int proj
 
 // One warp a (sequence, head, 8 columns of S); four lanes share a column and hold a quarter of its rows each (the
 // 16-byte groups of rows g with g mod 4 = the lane's part, so that the four parts read neighbouring words of shared
-// memory).  DP: the head size rounded up to a multiple of 32; rows of S beyond D stay zero.  The two dot products of a
+// memory; eight lanes a column were measured slower: a token's fixed work then weighs more than its sums).  DP: the head size rounded up to a multiple of 32; rows of S beyond D stay zero.  The two dot products of a
 // token are summed over a lane's rows first and over the four lanes after, in one fixed order.  The inputs of the next
 // tokens (seven, or three for heads over 128) are on their way into a ring in shared memory (cp.async) while the current token is computed.
 template <int DP>
@@ -161,28 +161,28 @@ delta_rule_kernel(const float* __restrict__ prep, int prep_stride, float* __rest
         const float* ks = cur;
         const float* qs = cur + DP;
         const float v = cur[2 * DP + (lane >> 2)], beta = cur[2 * DP + 8], g = cur[2 * DP + 9];
-        float sk0 = 0.0f, sk1 = 0.0f;
+        float sk0 = 0.0f, sk1 = 0.0f, sk2 = 0.0f, sk3 = 0.0f;
 #pragma unroll
         for (int j = 0; j < GROUPS; ++j) {
             const float4 k4 = *reinterpret_cast<const float4*>(ks + (4 * j + part) * 4);
             sk0 = fmaf(S[j][0], k4.x, sk0); sk1 = fmaf(S[j][1], k4.y, sk1);
-            sk0 = fmaf(S[j][2], k4.z, sk0); sk1 = fmaf(S[j][3], k4.w, sk1);
+            sk2 = fmaf(S[j][2], k4.z, sk2); sk3 = fmaf(S[j][3], k4.w, sk3);
         }
-        float sk = sk0 + sk1;
+        float sk = (sk0 + sk1) + (sk2 + sk3);
         sk += __shfl_xor_sync(0xffffffffu, sk, 1);
         sk += __shfl_xor_sync(0xffffffffu, sk, 2);
         const float u = beta * (v - g * sk);
-        float o0 = 0.0f, o1 = 0.0f;
+        float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
         for (int j = 0; j < GROUPS; ++j) {
             const float4 k4 = *reinterpret_cast<const float4*>(ks + (4 * j + part) * 4);
             const float4 q4 = *reinterpret_cast<const float4*>(qs + (4 * j + part) * 4);
             S[j][0] = fmaf(k4.x, u, g * S[j][0]); o0 = fmaf(S[j][0], q4.x, o0);
             S[j][1] = fmaf(k4.y, u, g * S[j][1]); o1 = fmaf(S[j][1], q4.y, o1);
-            S[j][2] = fmaf(k4.z, u, g * S[j][2]); o0 = fmaf(S[j][2], q4.z, o0);
-            S[j][3] = fmaf(k4.w, u, g * S[j][3]); o1 = fmaf(S[j][3], q4.w, o1);
+            S[j][2] = fmaf(k4.z, u, g * S[j][2]); o2 = fmaf(S[j][2], q4.z, o2);
+            S[j][3] = fmaf(k4.w, u, g * S[j][3]); o3 = fmaf(S[j][3], q4.w, o3);
         }
-        float o = o0 + o1;
+        float o = (o0 + o1) + (o2 + o3);
         o += __shfl_xor_sync(0xffffffffu, o, 1);
         o += __shfl_xor_sync(0xffffffffu, o, 2);
         if (live && part == 0) out[(size_t)row * H * V + head * V + col] = o;

@@ -4,6 +4,7 @@
 //
 //   hyper_read_norm   one block a row: u, then u / sqrt(mean(u^2) + eps) * gain, rounded once to the compute dtype.
 //   hyper_write       one thread an element of a row: the S old values are read, the S new ones written in place.
+//   hyper_write_read_norm   both for one row in one pass: a sub-layer's write-back and the next sub-layer's read.
 //   stream_sum        out[i] = sum_s X[s, index[i]]: what the model's last norm reads.
 // Also here: the squared ReLU of a feed-forward without a gate.
 #include "api.h"
@@ -14,7 +15,7 @@ namespace citlali {
 constexpr int kMaxStreams = 8;
 
 template <typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 hyper_read_norm_kernel(const float* __restrict__ X, size_t stream_stride, int S, const float* __restrict__ w_in,
                        const float* __restrict__ gain, TO* __restrict__ out, int W, float eps) {
     extern __shared__ float u[];
@@ -48,6 +49,40 @@ __global__ void hyper_write_kernel(float* __restrict__ X, size_t stream_stride, 
             X[t * stream_stride + e] = fmaf(w_out[t], yv, v);
         }
     }
+}
+
+// hyper_write for one row and, on the new values, the next sub-layer's hyper_read_norm: the streams are read once.
+template <typename TO>
+__global__ void __launch_bounds__(1024)
+hyper_write_read_norm_kernel(float* __restrict__ X, size_t stream_stride, int S, const float* __restrict__ y,
+                             const float* __restrict__ w_mix, const float* __restrict__ w_out,
+                             const float* __restrict__ w_in, const float* __restrict__ gain, TO* __restrict__ out, int W,
+                             float eps) {
+    extern __shared__ float u[];
+    __shared__ float scratch[32];
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.x;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const size_t e = (size_t)row * W + i;
+        float old[kMaxStreams];
+        for (int s = 0; s < S; ++s) old[s] = X[s * stream_stride + e];
+        const float yv = y[e];
+        float mixed = 0.0f;
+        for (int t = 0; t < S; ++t) {
+            float v = 0.0f;
+            for (int s = 0; s < S; ++s) v = fmaf(w_mix[s * S + t], old[s], v);
+            v = fmaf(w_out[t], yv, v);
+            X[t * stream_stride + e] = v;
+            mixed = fmaf(w_in[t], v, mixed);
+        }
+        u[i] = mixed;
+        ss = fmaf(mixed, mixed, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) stf(out, (size_t)row * W + i, u[i] * inv * gain[i]);
 }
 
 __global__ void stream_sum_kernel(const float* __restrict__ X, size_t stream_stride, int S,
@@ -93,7 +128,8 @@ extern "C" int citlali_hyper_read_norm(const float* X, size_t stream_stride, int
     return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(hyper_read_norm_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_kernel(hyper_read_norm_kernel<TO>, rows, 256, smem, stream, X, stream_stride, streams, w_in, gain, (TO*)out,
+        // few rows in bfloat16 (decoding): a row is spread over more threads; 32-bit keeps one order of summation
+        launch_kernel(hyper_read_norm_kernel<TO>, rows, (sizeof(TO) == 2 && rows < 128 && width >= 2048) ? 1024 : 256, smem, stream, X, stream_stride, streams, w_in, gain, (TO*)out,
                       width, eps);
         return CITLALI_LAUNCH_CHECK();
     });
@@ -108,6 +144,24 @@ extern "C" int citlali_hyper_write(float* X, size_t stream_stride, int streams, 
     }
     launch_kernel(hyper_write_kernel, grid_for(n), 256, 0, stream, X, stream_stride, streams, y, w_mix, w_out, n);
     return CITLALI_LAUNCH_CHECK();
+}
+
+extern "C" int citlali_hyper_write_read_norm(float* X, size_t stream_stride, int streams, const float* y, const float* w_mix,
+                                             const float* w_out, const float* w_in, const float* gain, void* out,
+                                             int out_dtype, int rows, int width, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (streams < 1 || streams > kMaxStreams || smem > 200 * 1024) {
+        set_last_error("hyper_write_read_norm: %d streams of width %d", streams, width);
+        return kBadShape;
+    }
+    return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(hyper_write_read_norm_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_kernel(hyper_write_read_norm_kernel<TO>, rows, (sizeof(TO) == 2 && rows < 128 && width >= 2048) ? 1024 : 256, smem, stream, X, stream_stride, streams, y, w_mix, w_out,
+                      w_in, gain, (TO*)out, width, eps);
+        return CITLALI_LAUNCH_CHECK();
+    });
 }
 
 extern "C" int citlali_stream_sum(const float* X, size_t stream_stride, int streams, const int32_t* index, float* out,

@@ -6,8 +6,9 @@
 // lo..pos in tiles of 64: the tile's rows are gathered from the pages into shared memory once (rows past pos are
 // zeros), warp w computes the scores of keys 16 w .. 16 w + 15, the row maxima and sums meet in shared memory, and
 // warp w accumulates the output columns R/4 w .. R/4 (w + 1).  Softmax is float32 (online, base 2); the sink joins
-// the denominator at the end.  What a row computes depends on its position and the window only, not on the step's
-// other rows.  Needs E a multiple of 16 and R a multiple of 64.
+// the denominator at the end.  In steps of few rows (decoding) a unit's tiles are dealt to several blocks in runs, whose
+// unnormalised sums, maxima and denominators a second kernel merges in run order; the number of runs follows the
+// number of rows in the step alone, so what else is in the step changes a row by rounding at most.  Needs E a multiple of 16 and R a multiple of 64.
 #include "api.h"
 #include "common.cuh"
 #include "mma_common.cuh"
@@ -23,7 +24,7 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
                             const int32_t* __restrict__ page_table, int table_stride,
                             const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
                             const float* __restrict__ sink, float* __restrict__ out, int rows, int H, int R, int E,
-                            int page_size, int window, float scale) {
+                            int page_size, int window, float scale, int splits, float* __restrict__ partial) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int ES = E + 8;                                   // row stride in elements: rows start 16 bytes apart in banks
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -34,13 +35,21 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
     wait_for_predecessor();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int groups = (H + 15) / 16;
-    const int row = blockIdx.x / groups, h0 = (blockIdx.x % groups) * 16;
+    const int unit = blockIdx.x / splits, split = blockIdx.x % splits;
+    const int row = unit / groups, h0 = (unit % groups) * 16;
     const int pos = row_pos[row];
     const int32_t* table = page_table + (size_t)row_slot[row] * table_stride;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    for (int idx = tid; idx < 16 * E; idx += 128) {
-        const int hh = idx / E, i = idx - hh * E;
-        Qs[hh * ES + i] = __float2bfloat16_rn(h0 + hh < H ? q[((size_t)row * H + h0 + hh) * E + i] : 0.0f);
+    {   // the queries of the sixteen heads, rounded to bfloat16: 16-byte loads, four elements a thread and turn
+        const int quads = E / 4;
+        for (int hh = 0; hh < 16; ++hh) {
+            const bool real = h0 + hh < H;
+            const float4* src = reinterpret_cast<const float4*>(q + ((size_t)row * H + h0 + hh) * E);
+            for (int i = tid; i < quads; i += 128) {
+                const float4 v = real ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<uint2*>(Qs + hh * ES + i * 4) = make_uint2(fa::pack_bf16(v.x, v.y), fa::pack_bf16(v.z, v.w));
+            }
+        }
     }
     const float sl2 = scale * 1.4426950408889634f;          // scores in units of log 2
     const int NT = R / 32;                                   // tiles of 8 output columns a warp owns
@@ -52,16 +61,20 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
     const int chunks = E / 8;                                // 16-byte pieces of a cached vector
     const uint32_t Qs_a = (uint32_t)__cvta_generic_to_shared(Qs), Ks_a = (uint32_t)__cvta_generic_to_shared(Ks),
                    Ps_a = (uint32_t)__cvta_generic_to_shared(Ps);
-    for (int t0 = lo; t0 <= pos; t0 += kTileKeys) {
+    // with several blocks a unit, this block walks a run of the unit's tiles; the runs are merged in their order
+    const int tiles = (pos - lo) / kTileKeys + 1, per = (tiles + splits - 1) / splits;
+    const int first = lo + split * per * kTileKeys;
+    const int last = min(pos, first + per * kTileKeys - 1);
+    for (int t0 = first; t0 <= last; t0 += kTileKeys) {
         __syncthreads();                                     // the tile before is no longer read; Q is in place
-        for (int c = tid; c < kTileKeys * chunks; c += 128) {
-            const int kr = c / chunks, ch = c - kr * chunks, key = t0 + kr;
-            __nv_bfloat16* dst = Ks + kr * ES + ch * 8;
+        for (int kr = tid >> 3; kr < kTileKeys; kr += 16) {      // eight threads a cached vector, sixteen vectors a pass
+            const int key = t0 + kr;
+            __nv_bfloat16* dst = Ks + kr * ES;
             if (key <= pos) {
-                const __nv_bfloat16* src = pool + ((size_t)table[key / page_size] * page_size + key % page_size) * E + ch * 8;
-                fa::cp_async16((uint32_t)__cvta_generic_to_shared(dst), src);
+                const __nv_bfloat16* src = pool + ((size_t)table[key / page_size] * page_size + key % page_size) * E;
+                for (int ch = tid & 7; ch < chunks; ch += 8) fa::cp_async16((uint32_t)__cvta_generic_to_shared(dst + ch * 8), src + ch * 8);
             } else {
-                *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+                for (int ch = tid & 7; ch < chunks; ch += 8) *reinterpret_cast<uint4*>(dst + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
             }
         }
         fa::cp_async_commit();
@@ -134,6 +147,23 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
             }
         }
     }
+    if (splits > 1) {
+        // unnormalised sums, the running maximum and the denominator of this run: [unit][split][16][R + 2]
+        float* dst = partial + ((size_t)unit * splits + split) * 16 * (R + 2);
+#pragma unroll
+        for (int n = 0; n < NTMAX; ++n) {
+            if (n < NT) {
+                const int col = col0 + n * 8 + t * 2;
+                *reinterpret_cast<float2*>(dst + g * (R + 2) + col) = make_float2(O[n][0], O[n][1]);
+                *reinterpret_cast<float2*>(dst + (g + 8) * (R + 2) + col) = make_float2(O[n][2], O[n][3]);
+            }
+        }
+        if (warp == 0 && t == 0) {
+            dst[g * (R + 2) + R] = m0; dst[g * (R + 2) + R + 1] = l0;
+            dst[(g + 8) * (R + 2) + R] = m1; dst[(g + 8) * (R + 2) + R + 1] = l1;
+        }
+        return;
+    }
     if (sink) {
         const float s0 = h0 + g < H ? sink[h0 + g] * 1.4426950408889634f : -INFINITY;
         const float s1 = h0 + g + 8 < H ? sink[h0 + g + 8] * 1.4426950408889634f : -INFINITY;
@@ -157,6 +187,31 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
     }
 }
 
+// The runs of a unit put together in run order: one block a (row, head), a thread a column at a time.
+__global__ void __launch_bounds__(128)
+latent_attention_merge_kernel(const float* __restrict__ partial, const float* __restrict__ sink, float* __restrict__ out,
+                              int H, int R, int splits) {
+    __shared__ float weight[64];
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int groups = (H + 15) / 16, row = blockIdx.x / H, h = blockIdx.x % H;
+    const int unit = row * groups + h / 16, hh = h % 16;
+    const float* src = partial + (size_t)unit * splits * 16 * (R + 2) + (size_t)hh * (R + 2);
+    const size_t run = (size_t)16 * (R + 2);
+    float top = sink ? sink[h] * 1.4426950408889634f : -INFINITY;
+    const float sk = top;
+    for (int s = 0; s < splits; ++s) top = fmaxf(top, src[s * run + R]);
+    float denom = sink ? fa::fast_exp2(sk - top) : 0.0f;
+    for (int s = 0; s < splits; ++s) denom += src[s * run + R + 1] * fa::fast_exp2(src[s * run + R] - top);   // an empty run: maximum -inf, counts nothing
+    if (threadIdx.x < splits) weight[threadIdx.x] = fa::fast_exp2(src[threadIdx.x * run + R] - top) / denom;
+    __syncthreads();
+    for (int i = threadIdx.x; i < R; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < splits; ++s) acc = fmaf(src[s * run + i], weight[s], acc);
+        out[((size_t)row * H + h) * R + i] = acc;
+    }
+}
+
 }  // namespace citlali
 
 using namespace citlali;
@@ -168,14 +223,22 @@ extern "C" int citlali_latent_attention_mma_supports(int R, int E) {
 extern "C" int citlali_latent_attention_mma(const float* q, const void* pool, const int32_t* page_table, int table_stride,
                                             const int32_t* row_slot, const int32_t* row_pos, const float* sink, float* out,
                                             int rows, int H, int R, int E, int page_size, int window, float scale,
-                                            cudaStream_t stream) {
+                                            int splits, float* partial, size_t partial_floats, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (!citlali_latent_attention_mma_supports(R, E)) {
         set_last_error("latent_attention_mma: a latent of %d in a cached vector of %d (multiples of 64 and 16, at most 512 and 1024)", R, E);
         return kBadShape;
     }
     const size_t smem = (size_t)(16 + kTileKeys) * (E + 8) * 2 + 16 * kPStride * 2 + 2 * 4 * 16 * sizeof(float);
-    const long blocks = (long)rows * ((H + 15) / 16);
+    const long units = (long)rows * ((H + 15) / 16);
+    if (splits < 1) splits = 1;
+    if (splits > 64) splits = 64;
+    if (splits > 1 && (size_t)units * splits * 16 * (R + 2) > partial_floats) {
+        set_last_error("latent_attention_mma: %d runs a unit need %zu floats of scratch, %zu were given", splits,
+                       (size_t)units * splits * 16 * (R + 2), partial_floats);
+        return kBadShape;
+    }
+    const long blocks = units * splits;
     if (blocks > 0x7fffffffL) {
         set_last_error("latent_attention_mma: %d rows of %d heads exceed the grid", rows, H);
         return kTooLarge;
@@ -184,12 +247,16 @@ extern "C" int citlali_latent_attention_mma(const float* q, const void* pool, co
     do {                                                                                                                 \
         cudaFuncSetAttribute(latent_attention_mma_kernel<NTMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         launch_kernel(latent_attention_mma_kernel<NTMAX>, (int)blocks, 128, smem, stream, q, (const __nv_bfloat16*)pool,  \
-                      page_table, table_stride, row_slot, row_pos, sink, out, rows, H, R, E, page_size, window, scale);   \
+                      page_table, table_stride, row_slot, row_pos, sink, out, rows, H, R, E, page_size, window, scale,    \
+                      splits, partial);                                                                                  \
     } while (0)
     const int nt = R / 32;
     if (nt <= 4) CITLALI_LATENT_MMA(4);
     else if (nt <= 8) CITLALI_LATENT_MMA(8);
     else CITLALI_LATENT_MMA(16);
 #undef CITLALI_LATENT_MMA
+    int code = CITLALI_LAUNCH_CHECK();
+    if (code != 0 || splits == 1) return code;
+    launch_kernel(latent_attention_merge_kernel, rows * H, 128, 0, stream, (const float*)partial, sink, out, H, R, splits);
     return CITLALI_LAUNCH_CHECK();
 }

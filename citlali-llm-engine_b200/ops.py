@@ -461,6 +461,19 @@ def hyper_write(X: torch.Tensor, y: torch.Tensor, w_mix: torch.Tensor, w_out: to
                                      _sz(rows * width), _stream()), "hyper_write")
 
 
+def hyper_write_read_norm(X, y, w_mix, w_out, w_in, gain, eps, out):
+    """:func:`hyper_write` of one sub-layer and :func:`hyper_read_norm` of the next in one pass over the streams."""
+    _need_cuda(X, y, w_mix, w_out, w_in, gain, out)
+    S, rows, width = X.shape
+    require(X.dtype == torch.float32 and y.dtype == torch.float32 and y.shape == (rows, width)
+            and w_mix.dtype == torch.float32 and w_mix.shape == (S, S) and w_out.dtype == torch.float32 and w_out.numel() == S
+            and w_in.dtype == torch.float32 and w_in.numel() == S and gain.dtype == torch.float32 and gain.numel() == width
+            and out.shape == (rows, width), "hyper_write_read_norm: shapes or dtypes do not fit")
+    _check(lib().citlali_hyper_write_read_norm(_ptr(X), _sz(rows * width), _i(S), _ptr(y), _ptr(w_mix), _ptr(w_out),
+                                               _ptr(w_in), _ptr(gain), _ptr(out), _i(_dtype_code(out)), _i(rows),
+                                               _i(width), _f(eps), _stream()), "hyper_write_read_norm")
+
+
 def stream_sum(X: torch.Tensor, out: torch.Tensor, row_index: Optional[torch.Tensor] = None):
     """``out[i] = sum_s X[s, row_index[i]]``."""
     _need_cuda(X, out, row_index)
@@ -549,8 +562,11 @@ def heads_product(x, x_row, x_head, M, m_head, m_k, m_n, y, y_row, y_head, rows,
         _i(rot_dims), _ptr(row_pos), _ptr(gate), _sz(gate_stride), _stream()), "heads_product")
 
 
+_KERNELS_PER_CALL["latent_attention_mma_runs"] = 2
+
+
 def latent_attention(q, pool, page_table, row_slot, row_pos, sink, out, H, R, E, page_size, window, scale,
-                     tensor_cores=None):
+                     tensor_cores=None, splits=None):
     """The walk over a latent cache.  A bfloat16 cache whose sizes the tensor-core kernel takes runs that kernel
     (``tensor_cores`` False: never), everything else the one on CUDA cores, which is exact in 32-bit."""
     _need_cuda(q, pool, page_table, row_slot, row_pos, sink, out)
@@ -560,10 +576,20 @@ def latent_attention(q, pool, page_table, row_slot, row_pos, sink, out, H, R, E,
             and sink.numel() == H)), "latent_attention: shapes or dtypes do not fit")
     if (tensor_cores is not False and pool.dtype == torch.bfloat16
             and lib().citlali_latent_attention_mma_supports(_i(R), _i(E))):
+        # few rows (decoding): a unit's key tiles go to several blocks, so that the device is busy; the number of runs
+        # follows the number of rows alone and never exceeds the tiles a window (or the longest sequence) has
+        units = rows * ((H + 15) // 16)
+        longest = int(window) if window else page_table.shape[1] * page_size
+        splits = max(1, min(sm_count(q.device) * 2 // units, (longest + 63) // 64, 32)) if splits is None else int(splits)
+        partial = None
+        if splits > 1:
+            partial = _scratch(q.device, "latent_attention runs", units * splits * 16 * (R + 2) * 4)
         _check(lib().citlali_latent_attention_mma(_ptr(q), _ptr(pool), _ptr(page_table), _i(page_table.shape[1]),
                                                   _ptr(row_slot), _ptr(row_pos), _ptr(sink), _ptr(out), _i(rows), _i(H),
-                                                  _i(R), _i(E), _i(page_size), _i(int(window or 0)), _f(scale), _stream()),
-               "latent_attention_mma")
+                                                  _i(R), _i(E), _i(page_size), _i(int(window or 0)), _f(scale), _i(splits),
+                                                  _ptr(partial), _sz(partial.numel() // 4 if partial is not None else 0),
+                                                  _stream()),
+               "latent_attention_mma" if splits == 1 else "latent_attention_mma_runs")
         return
     require(tensor_cores is not True, "latent_attention: the tensor-core kernel does not take this cache")
     _check(lib().citlali_latent_attention(_ptr(q), _ptr(pool), _i(_dtype_code(pool)), _ptr(page_table),

@@ -115,6 +115,10 @@ class StepBatch:
     # not know of it breaks the chain instead of passing on something stale.
     norm_carry: Optional["NormedRows"] = None
     norm_carry_in: Optional["NormedRows"] = None
+    # A block on several residual streams may leave its last write-back undone, as (y, mix, out), for the next such
+    # block to do together with its first read (one pass over the streams instead of two); the model does what is left
+    # after the last layer.
+    stream_write: Optional[tuple] = None
 
     @property
     def rows(self) -> int:

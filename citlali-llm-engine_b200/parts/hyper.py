@@ -8,7 +8,9 @@ Instead of one residual x there are S copies X_1 .. X_S (float32, ``[S, rows, hi
 
 With S = 1 and in = out = mix = 1 this is the pre-norm residual layer.  The mixture u, the norm and the write-back are
 32-bit: one kernel reads the streams and leaves the normed rows in the compute dtype (``ops.hyper_read_norm``), one
-updates all streams in place (``ops.hyper_write``).  The sub-layer's parts are the ones any block uses: they add their
+updates all streams in place (``ops.hyper_write``); a write-back and the read that follows it, in this layer or the next,
+are one pass over the streams (``ops.hyper_write_read_norm``; the last write-back of a layer is left in
+``batch.stream_write`` for whoever comes next).  The sub-layer's parts are the ones any block uses: they add their
 output into a float32 buffer, which here is a fresh one (a part that says ``can_overwrite`` is told to store instead of
 add and spares the zero fill).  The norm must be an RMS norm (its sum of squares is taken inside the read kernel).
 
@@ -29,6 +31,8 @@ from .norm import RMSNorm
 
 
 class HyperConnectionBlock:
+    takes_stream_write = True        # does the write-back the block ahead left in ``batch.stream_write``
+
     def __init__(self, layer_spec):
         has = layer_spec.parts.__contains__
         params = layer_spec.block_params
@@ -75,10 +79,14 @@ class HyperConnectionBlock:
     def forward(self, X, batch, cache_view, write_cache=True):
         S, rows, hidden = X.shape
         require(S == self.residual_streams, f"the layer takes {self.residual_streams} streams, got {S}")
+        pending, batch.stream_write = batch.stream_write, None        # (y, mix, out) of the sub-layer before, not yet applied
         for role, norm, part, _ in self.subs:
             w_in, w_out, w_mix = self.weights[role]
             h = torch.empty((rows, hidden), dtype=self.dtype, device=X.device)
-            ops.hyper_read_norm(X, w_in, self.gains[role], norm.eps, h)
+            if pending is None:
+                ops.hyper_read_norm(X, w_in, self.gains[role], norm.eps, h)
+            else:
+                ops.hyper_write_read_norm(X, pending[0], pending[1], pending[2], w_in, self.gains[role], norm.eps, h)
             fresh = bool(getattr(part, "can_overwrite", False))
             y = (torch.empty if fresh else torch.zeros)((rows, hidden), dtype=torch.float32, device=X.device)
             extra = {"overwrite": True} if fresh else {}
@@ -86,7 +94,8 @@ class HyperConnectionBlock:
                 part.forward(h, batch, cache_view, y, write_cache, **extra)
             else:
                 part.forward(h, batch, y, **extra)
-            ops.hyper_write(X, y, w_mix, w_out)
+            pending = (y, w_mix, w_out)
+        batch.stream_write = pending
         return X
 
 

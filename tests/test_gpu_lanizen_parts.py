@@ -112,6 +112,12 @@ def test_stream_kernels(dtype, S, width):
     Xd = X.to(DEV).clone()
     ops.hyper_write(Xd, y.to(DEV), w_mix.to(DEV), w_out.to(DEV))
     close(Xd, plain.hyper_write(X.double(), y.double(), w_mix, w_out), torch.float32)
+    # the write-back and the next read in one pass: the same bits as the two kernels one after the other
+    w_in2 = torch.randn(S)
+    Xf, h2, h2f = X.to(DEV).clone(), torch.empty_like(h), torch.empty_like(h)
+    ops.hyper_write_read_norm(Xf, y.to(DEV), w_mix.to(DEV), w_out.to(DEV), w_in2.to(DEV), gain.to(DEV), 1e-5, h2f)
+    ops.hyper_read_norm(Xd, w_in2.to(DEV), gain.to(DEV), 1e-5, h2)
+    assert torch.equal(Xf, Xd) and torch.equal(h2f, h2)
     idx = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
     out = torch.empty(3, width, device=DEV)
     ops.stream_sum(X.to(DEV), out, idx)
@@ -406,10 +412,37 @@ def test_tensor_core_walk_window_edges_and_far_key(window):
 
 
 def test_tensor_core_walk_does_not_depend_on_the_batch():
-    """A row's result is the same bits alone and among other rows, in any order, whatever pages it lies in."""
+    """A row's result is the same bits among other rows in any order, whatever pages it lies in and whatever the other
+    rows are; in a step of another size (whose rows' keys are dealt to blocks in other runs) it differs by rounding."""
     H, R, E, T = 8, 64, 80, 300
     keys = torch.randn(T, E).to(torch.bfloat16).float()
     q = torch.randn(4, H * E)
-    a = _latent_walk(q, keys, list(range(5)), [299, 10, 150, 64], None, H, R, E, 100, 0.2, dtype=torch.bfloat16)
-    b = _latent_walk(q[[2, 0]], keys, [4, 2, 0, 1, 3], [150, 299], None, H, R, E, 100, 0.2, dtype=torch.bfloat16)
+    sink = torch.randn(H)
+    a = _latent_walk(q, keys, list(range(5)), [299, 10, 150, 64], sink, H, R, E, 100, 0.2, dtype=torch.bfloat16)
+    b = _latent_walk(q[[2, 0, 0, 1]], keys, [4, 2, 0, 1, 3], [150, 299, 7, 40], sink, H, R, E, 100, 0.2, dtype=torch.bfloat16)
     assert torch.equal(a[2], b[0]) and torch.equal(a[0], b[1])
+    alone = _latent_walk(q[:1], keys, [3, 1, 4, 0, 2], [299], sink, H, R, E, 100, 0.2, dtype=torch.bfloat16)
+    assert torch.allclose(alone[0], a[0], atol=2e-3)
+    want = _walk_plain(q, keys, [299, 10, 150, 64], sink, H, R, E, 100, 0.2)
+    close(a, want, torch.bfloat16, bf16=1e-2)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 8])
+def test_tensor_core_walk_in_runs(splits):
+    """The keys of a row dealt to several blocks and merged: every number of runs, also more runs than tiles."""
+    H, R, E, T = 20, 128, 192, 330
+    keys = (0.5 * torch.randn(T, E)).to(torch.bfloat16).float()
+    positions = [T - 1, 0, 64, 200]
+    q = torch.randn(len(positions), H * E)
+    sink = torch.randn(H)
+    pool = torch.zeros(7, 64, E, dtype=torch.bfloat16)
+    order = [5, 0, 3, 1, 6, 2]
+    for t_ in range(T):
+        pool[order[t_ // 64], t_ % 64] = keys[t_].to(torch.bfloat16)
+    for window in (0, 150):
+        out = torch.empty(len(positions), H * R, device=DEV)
+        ops.latent_attention(q.to(DEV), pool.to(DEV), torch.tensor([order], dtype=torch.int32, device=DEV),
+                             torch.zeros(len(positions), dtype=torch.int32, device=DEV),
+                             torch.tensor(positions, dtype=torch.int32, device=DEV), sink.to(DEV), out, H, R, E, 64, window,
+                             0.1, splits=splits)
+        close(out, _walk_plain(q, keys, positions, sink, H, R, E, window, 0.1), torch.bfloat16, bf16=1e-2)
