@@ -19,6 +19,10 @@ void citlali_set_dependent_launch(int enabled);
 int citlali_embed_rows(const void* table, int table_dtype, const int32_t* tokens, float* out,
                        int rows, int hidden, int vocab, float scale, int32_t* error_flag, cudaStream_t stream);
 
+// The same into `copies` buffers `copy_stride` elements apart (the residual streams of a model that has several).
+int citlali_embed_rows_copies(const void* table, int table_dtype, const int32_t* tokens, float* out, int rows, int hidden,
+                              int vocab, float scale, int32_t* error_flag, int copies, size_t copy_stride, cudaStream_t stream);
+
 // rows_out = bfloat16(x) [rows, hidden] and sumsq[r, g] = sum of x[r, 32 g .. 32 g + 31]^2 (hidden a multiple of 32):
 // what citlali_gemm_tc_normed's `scale_sumsq` reads, for rows that did not come out of an emitting product.
 int citlali_norm_inputs(const float* x, void* rows_out, float* sumsq, int rows, int hidden, cudaStream_t stream);

@@ -7,7 +7,7 @@
 // state and the outputs do not depend on how a sequence was cut into steps.
 //
 // Three kernels:
-//   delta_prepare   one block a row: the short causal convolution over time of the q, k, v channels (earlier tokens
+//   delta_prepare   one block a (row, q head / k head / head's values): the short causal convolution over time of the q, k, v channels (earlier tokens
 //                   from the step's rows or, before its first row, from the sequence's kept inputs), SiLU, unit length
 //                   for q and k heads, beta = sigmoid(.), g = exp(-exp(A_log) softplus(. + dt_bias)).  All float32.
 //                   A second launch then moves the sequence's last taps-1 inputs into its state.
@@ -29,21 +29,27 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
 // proj [rows, proj_stride] float32 holds, per row: q (KH*D) | k (KH*D) | v (H*V) | gate (H*V) | b (H) | a (H).
 // prep [rows, C + 2H] receives q^ | k^ | v | beta | g, C = 2 KH D + H V.
 // conv_state [slot] is [taps-1, C]: the inputs at the sequence's last taps-1 positions, oldest first.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 delta_prepare_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ taps_w, int taps,
                      const float* __restrict__ state, size_t state_stride, size_t conv_off,
                      const int32_t* __restrict__ row_slot, const float* __restrict__ a_log,
                      const float* __restrict__ dt_bias, float* __restrict__ prep, int H, int KH, int D, int V, float unit_eps) {
-    extern __shared__ float act[];          // C floats
+    extern __shared__ float act[];          // max(D, V) floats
+    __shared__ float scratch[32];
     dependents_may_launch();
     wait_for_predecessor();
-    const int row = blockIdx.x;
+    // A block: one row and one segment of its channels: a q head, a k head, or a head's values.
+    const int row = blockIdx.x, seg = blockIdx.y;
     const int C = 2 * KH * D + H * V;
+    const bool unit = seg < 2 * KH;                           // q and k heads are made unit vectors
+    const int c0 = unit ? seg * D : 2 * KH * D + (seg - 2 * KH) * V, n = unit ? D : V;
     const int slot = row_slot[row];
     int in_step = 0;                        // how many of the tokens before this one are rows of this step
     while (in_step < taps - 1 && row - in_step - 1 >= 0 && row_slot[row - in_step - 1] == slot) ++in_step;
     const float* kept = state + (size_t)slot * state_stride + conv_off;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int c = c0 + i;
         float acc = 0.0f;
         for (int j = taps - 1; j >= 0; --j) {                 // j tokens back; oldest first
             float x;
@@ -51,26 +57,24 @@ delta_prepare_kernel(const float* __restrict__ proj, int proj_stride, const floa
             else x = kept[(size_t)(taps - 1 - j + in_step) * C + c];
             acc = fmaf(taps_w[(size_t)c * taps + (taps - 1 - j)], x, acc);
         }
-        act[c] = siluf_(acc);
+        const float v = siluf_(acc);
+        act[i] = v;
+        ss = fmaf(v, v, ss);
     }
-    __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    for (int head = warp; head < 2 * KH; head += warps) {     // q heads, then k heads
-        float* v = act + head * D;
-        float ss = 0.0f;
-        for (int i = lane; i < D; i += 32) ss = fmaf(v[i], v[i], ss);
-        ss = warp_sum(ss);
-        float f = 1.0f / sqrtf(ss + unit_eps);
-        if (head < KH) f /= sqrtf((float)D);
-        for (int i = lane; i < D; i += 32) v[i] *= f;
+    float f = 1.0f;
+    if (unit) {
+        ss = block_sum(ss, scratch);
+        f = 1.0f / sqrtf(ss + unit_eps);
+        if (seg < KH) f /= sqrtf((float)D);
     }
-    __syncthreads();
     float* dst = prep + (size_t)row * (C + 2 * H);
-    for (int c = threadIdx.x; c < C; c += blockDim.x) dst[c] = act[c];
-    const float* rest = proj + (size_t)row * proj_stride + C + H * V;
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
-        dst[C + h] = sigmoidf_(rest[h]);
-        dst[C + H + h] = expf(-expf(a_log[h]) * softplusf_(rest[H + h] + dt_bias[h]));
+    for (int i = threadIdx.x; i < n; i += blockDim.x) dst[c0 + i] = act[i] * f;      // a thread reads back what it wrote
+    if (seg == 0) {
+        const float* rest = proj + (size_t)row * proj_stride + C + H * V;
+        for (int h = threadIdx.x; h < H; h += blockDim.x) {
+            dst[C + h] = sigmoidf_(rest[h]);
+            dst[C + H + h] = expf(-expf(a_log[h]) * softplusf_(rest[H + h] + dt_bias[h]));
+        }
     }
 }
 
@@ -234,13 +238,13 @@ extern "C" int citlali_delta_prepare(const float* proj, int proj_stride, const f
         return kBadShape;
     }
     const int C = 2 * KH * D + H * V;
-    const size_t smem = (size_t)C * sizeof(float);
-    if (smem > 200 * 1024) {
-        set_last_error("delta_prepare: %d convolved channels do not fit in shared memory", C);
+    const size_t smem = (size_t)(D > V ? D : V) * sizeof(float);
+    if (smem > 48 * 1024 || 2 * KH + H > 65535) {
+        set_last_error("delta_prepare: heads of %d and values of %d, or %d segments a row, are too many", D, V, 2 * KH + H);
         return kTooLarge;
     }
-    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_kernel(delta_prepare_kernel, rows, 256, smem, stream, proj, proj_stride, taps_w, taps, (const float*)state,
+    dim3 prepare_grid(rows, 2 * KH + H);
+    launch_kernel(delta_prepare_kernel, prepare_grid, 128, smem, stream, proj, proj_stride, taps_w, taps, (const float*)state,
                   state_stride, conv_off, row_slot, a_log, dt_bias, prep, H, KH, D, V, unit_eps);
     int code = CITLALI_LAUNCH_CHECK();
     if (code != 0 || taps == 1) return code;

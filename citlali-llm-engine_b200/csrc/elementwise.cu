@@ -25,7 +25,8 @@ void set_last_error(const char* fmt, ...) {
 // A token outside the vocabulary is not read: the row is zeroed and the flag is raised.
 template <typename TW>
 __global__ void embed_rows_kernel(const TW* __restrict__ table, const int32_t* __restrict__ tokens,
-                                  float* __restrict__ out, int hidden, int vocab, float scale, int32_t* error_flag) {
+                                  float* __restrict__ out, int hidden, int vocab, float scale, int32_t* error_flag,
+                                  int copies, size_t copy_stride) {
     dependents_may_launch();
     wait_for_predecessor();
     const int row = blockIdx.x;
@@ -34,7 +35,10 @@ __global__ void embed_rows_kernel(const TW* __restrict__ table, const int32_t* _
     if (!ok && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
     const TW* src = table + (size_t)(ok ? tok : 0) * hidden;
     float* dst = out + (size_t)row * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? ldf(src, i) * scale : 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = ok ? ldf(src, i) * scale : 0.0f;
+        for (int c = 0; c < copies; ++c) dst[c * copy_stride + i] = v;         // every residual stream starts as this row
+    }
 }
 
 // What a layer norm that lives in the products around it needs of rows it has not seen come out of a product: the rows
@@ -165,13 +169,20 @@ extern "C" const char* citlali_last_error(void) { return g_last_error; }
 // start early and wait on the device for their predecessor (programmatic dependent launch).
 extern "C" void citlali_set_dependent_launch(int enabled) { g_dependent_launch = enabled != 0; }
 
-extern "C" int citlali_embed_rows(const void* table, int table_dtype, const int32_t* tokens, float* out,
-                                  int rows, int hidden, int vocab, float scale, int32_t* error_flag, cudaStream_t stream) {
-    if (rows <= 0) return 0;
+extern "C" int citlali_embed_rows_copies(const void* table, int table_dtype, const int32_t* tokens, float* out,
+                                         int rows, int hidden, int vocab, float scale, int32_t* error_flag, int copies,
+                                         size_t copy_stride, cudaStream_t stream) {
+    if (rows <= 0 || copies <= 0) return 0;
     return CITLALI_DISPATCH_FLOAT(table_dtype, TW, [&] {
-        launch_kernel(embed_rows_kernel<TW>, rows, 256, 0, stream, (const TW*)table, tokens, out, hidden, vocab, scale, error_flag);
+        launch_kernel(embed_rows_kernel<TW>, rows, 256, 0, stream, (const TW*)table, tokens, out, hidden, vocab, scale, error_flag,
+                      copies, copy_stride);
         return CITLALI_LAUNCH_CHECK();
     });
+}
+
+extern "C" int citlali_embed_rows(const void* table, int table_dtype, const int32_t* tokens, float* out,
+                                  int rows, int hidden, int vocab, float scale, int32_t* error_flag, cudaStream_t stream) {
+    return citlali_embed_rows_copies(table, table_dtype, tokens, out, rows, hidden, vocab, scale, error_flag, 1, 0, stream);
 }
 
 extern "C" int citlali_norm_inputs(const float* x, void* rows_out, float* sumsq, int rows, int hidden, cudaStream_t stream) {

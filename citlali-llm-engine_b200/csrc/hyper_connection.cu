@@ -18,17 +18,30 @@ template <typename TO>
 __global__ void __launch_bounds__(1024)
 hyper_read_norm_kernel(const float* __restrict__ X, size_t stream_stride, int S, const float* __restrict__ w_in,
                        const float* __restrict__ gain, TO* __restrict__ out, int W, float eps) {
-    extern __shared__ float u[];
+    extern __shared__ __align__(16) float u[];
     __shared__ float scratch[32];
     dependents_may_launch();
     wait_for_predecessor();
     const int row = blockIdx.x;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        float v = 0.0f;
-        for (int s = 0; s < S; ++s) v = fmaf(w_in[s], X[s * stream_stride + (size_t)row * W + i], v);
-        u[i] = v;
-        ss = fmaf(v, v, ss);
+    if (W % 4 == 0 && stream_stride % 4 == 0) {               // four features a thread and turn, 16-byte loads
+        for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < S; ++s) {
+                const float4 xv = *reinterpret_cast<const float4*>(X + s * stream_stride + (size_t)row * W + i);
+                const float w = w_in[s];
+                v.x = fmaf(w, xv.x, v.x); v.y = fmaf(w, xv.y, v.y); v.z = fmaf(w, xv.z, v.z); v.w = fmaf(w, xv.w, v.w);
+            }
+            *reinterpret_cast<float4*>(u + i) = v;
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < W; i += blockDim.x) {
+            float v = 0.0f;
+            for (int s = 0; s < S; ++s) v = fmaf(w_in[s], X[s * stream_stride + (size_t)row * W + i], v);
+            u[i] = v;
+            ss = fmaf(v, v, ss);
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)W + eps);
@@ -58,27 +71,52 @@ hyper_write_read_norm_kernel(float* __restrict__ X, size_t stream_stride, int S,
                              const float* __restrict__ w_mix, const float* __restrict__ w_out,
                              const float* __restrict__ w_in, const float* __restrict__ gain, TO* __restrict__ out, int W,
                              float eps) {
-    extern __shared__ float u[];
+    extern __shared__ __align__(16) float u[];
     __shared__ float scratch[32];
     dependents_may_launch();
     wait_for_predecessor();
     const int row = blockIdx.x;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        const size_t e = (size_t)row * W + i;
-        float old[kMaxStreams];
-        for (int s = 0; s < S; ++s) old[s] = X[s * stream_stride + e];
-        const float yv = y[e];
-        float mixed = 0.0f;
-        for (int t = 0; t < S; ++t) {
-            float v = 0.0f;
-            for (int s = 0; s < S; ++s) v = fmaf(w_mix[s * S + t], old[s], v);
-            v = fmaf(w_out[t], yv, v);
-            X[t * stream_stride + e] = v;
-            mixed = fmaf(w_in[t], v, mixed);
+    if (W % 4 == 0 && stream_stride % 4 == 0) {               // four features a thread and turn, 16-byte loads and stores
+        for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+            const size_t e = (size_t)row * W + i;
+            float4 old[kMaxStreams];
+            for (int s = 0; s < S; ++s) old[s] = *reinterpret_cast<const float4*>(X + s * stream_stride + e);
+            const float4 yv = *reinterpret_cast<const float4*>(y + e);
+            float4 mixed = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int t = 0; t < S; ++t) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int s = 0; s < S; ++s) {
+                    const float m = w_mix[s * S + t];
+                    v.x = fmaf(m, old[s].x, v.x); v.y = fmaf(m, old[s].y, v.y); v.z = fmaf(m, old[s].z, v.z); v.w = fmaf(m, old[s].w, v.w);
+                }
+                const float o = w_out[t], wi = w_in[t];
+                v.x = fmaf(o, yv.x, v.x); v.y = fmaf(o, yv.y, v.y); v.z = fmaf(o, yv.z, v.z); v.w = fmaf(o, yv.w, v.w);
+                *reinterpret_cast<float4*>(X + t * stream_stride + e) = v;
+                mixed.x = fmaf(wi, v.x, mixed.x); mixed.y = fmaf(wi, v.y, mixed.y);
+                mixed.z = fmaf(wi, v.z, mixed.z); mixed.w = fmaf(wi, v.w, mixed.w);
+            }
+            *reinterpret_cast<float4*>(u + i) = mixed;
+            ss = fmaf(mixed.x, mixed.x, ss); ss = fmaf(mixed.y, mixed.y, ss);
+            ss = fmaf(mixed.z, mixed.z, ss); ss = fmaf(mixed.w, mixed.w, ss);
         }
-        u[i] = mixed;
-        ss = fmaf(mixed, mixed, ss);
+    } else {
+        for (int i = threadIdx.x; i < W; i += blockDim.x) {
+            const size_t e = (size_t)row * W + i;
+            float old[kMaxStreams];
+            for (int s = 0; s < S; ++s) old[s] = X[s * stream_stride + e];
+            const float yv = y[e];
+            float mixed = 0.0f;
+            for (int t = 0; t < S; ++t) {
+                float v = 0.0f;
+                for (int s = 0; s < S; ++s) v = fmaf(w_mix[s * S + t], old[s], v);
+                v = fmaf(w_out[t], yv, v);
+                X[t * stream_stride + e] = v;
+                mixed = fmaf(w_in[t], v, mixed);
+            }
+            u[i] = mixed;
+            ss = fmaf(mixed, mixed, ss);
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)W + eps);

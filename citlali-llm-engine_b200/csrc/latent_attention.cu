@@ -9,7 +9,8 @@
 //                      row's position (pairs (2i, 2i+1), angle = float(position) * inv_freq[i]), cache write.
 //   heads_product      y[row, h, :] = x[row, h, :] . M_h for a matrix per head given by strides (W_uk as stored, or
 //                      W_uv transposed); optional extras: a tail of the row rotated and copied behind the product
-//                      (the query's rotated part), or a sigmoid gate on the result.
+//                      (the query's rotated part), or a sigmoid gate on the result.  bfloat16 matrices run on the
+//                      tensor cores (heads_product_mma), float32 ones on CUDA cores.
 //   latent_attention   one warp a (row, head): keys lo..pos in ascending order, lo = 0 or pos - window + 1, online
 //                      softmax in float32 whose denominator also counts exp(sink) once.
 #include "api.h"
@@ -140,16 +141,18 @@ heads_product_kernel(const TX* __restrict__ x, size_t x_row, int x_head, const T
 }
 
 // The same product on the tensor cores for bfloat16 matrices: a block of four warps computes 64 rows x 64 columns of one
-// head (a warp: 16 rows), x and M_h pass through shared memory as bfloat16 in tiles of 32 k (M_h laid [n][k] whatever
-// its strides), m16n8k16 MMAs with float accumulators, k ascending.
+// head (a warp: 16 rows), x and M_h pass through shared memory as bfloat16 in tiles of 64 k (M_h laid [n][k] whatever
+// its strides; 16-byte loads along the matrix's contiguous axis where alignment allows), m16n8k16 MMAs with float
+// accumulators, k ascending.
 template <typename TX, typename TY>
 __global__ void __launch_bounds__(128)
 heads_product_mma_kernel(const TX* __restrict__ x, size_t x_row, int x_head, const __nv_bfloat16* __restrict__ M,
                          size_t m_head, int m_k, int m_n, TY* __restrict__ y, size_t y_row, int y_head, int rows, int K,
                          int N, int tail, const float* __restrict__ inv_freq, int rot_dims,
                          const int32_t* __restrict__ row_pos, const float* __restrict__ gate, size_t gate_stride) {
-    __shared__ __align__(16) __nv_bfloat16 xs[64][40];
-    __shared__ __align__(16) __nv_bfloat16 ms[64][40];
+    constexpr int KT = 64, LD = KT + 8;
+    __shared__ __align__(16) __nv_bfloat16 xs[64][LD];
+    __shared__ __align__(16) __nv_bfloat16 ms[64][LD];
     dependents_may_launch();
     wait_for_predecessor();
     const int h = blockIdx.y, row0 = blockIdx.x * 64, n0 = blockIdx.z * 64;
@@ -158,26 +161,61 @@ heads_product_mma_kernel(const TX* __restrict__ x, size_t x_row, int x_head, con
 #pragma unroll
     for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
     const uint32_t xs_a = (uint32_t)__cvta_generic_to_shared(&xs[0][0]), ms_a = (uint32_t)__cvta_generic_to_shared(&ms[0][0]);
-    for (int k0 = 0; k0 < K; k0 += 32) {
-        for (int e = threadIdx.x; e < 64 * 32; e += 128) {
-            const int r = e >> 5, k = e & 31;
-            xs[r][k] = __float2bfloat16_rn((row0 + r < rows && k0 + k < K)
-                                           ? ldf(x, (size_t)(row0 + r) * x_row + (size_t)h * x_head + k0 + k) : 0.0f);
+    const __nv_bfloat16* Mh = M + (size_t)h * m_head;
+    const bool x_vec = sizeof(TX) == 4 && x_row % 4 == 0 && x_head % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    const bool m_vec = (reinterpret_cast<uintptr_t>(M) & 15) == 0 && m_head % 8 == 0 && (m_k == 1 ? m_n % 8 == 0 : m_k % 8 == 0);
+    const __nv_bfloat16 zero = __float2bfloat16_rn(0.0f);
+    for (int k0 = 0; k0 < K; k0 += KT) {
+        // x: 64 rows x 64 k in pieces of four
+        for (int e = threadIdx.x; e < 64 * (KT / 4); e += 128) {
+            const int r = e / (KT / 4), k = (e % (KT / 4)) * 4, row = row0 + r;
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (row < rows) {
+                const TX* src = x + (size_t)row * x_row + (size_t)h * x_head + k0 + k;
+                if constexpr (sizeof(TX) == 4) {
+                    if (x_vec && k0 + k + 4 <= K) {
+                        const float4 f = *reinterpret_cast<const float4*>(src);
+                        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+                    } else {
+                        for (int j = 0; j < 4; ++j) if (k0 + k + j < K) v[j] = ldf(src, j);
+                    }
+                } else {
+                    for (int j = 0; j < 4; ++j) if (k0 + k + j < K) v[j] = ldf(src, j);
+                }
+            }
+            *reinterpret_cast<uint2*>(&xs[r][k]) = make_uint2(fa::pack_bf16(v[0], v[1]), fa::pack_bf16(v[2], v[3]));
         }
-        for (int e = threadIdx.x; e < 64 * 32; e += 128) {
-            const int k = m_n == 1 ? e >> 6 : e & 31, n = m_n == 1 ? e & 63 : e >> 5;     // the matrix's contiguous axis first
-            ms[n][k] = (k0 + k < K && n0 + n < N) ? M[(size_t)h * m_head + (size_t)(k0 + k) * m_k + (size_t)(n0 + n) * m_n]
-                                                  : __float2bfloat16_rn(0.0f);
+        // M_h: 64 n x 64 k in pieces of eight along the matrix's contiguous axis
+        for (int e = threadIdx.x; e < 64 * (KT / 8); e += 128) {
+            if (m_k == 1) {                                   // k contiguous: a piece is eight k of one n
+                const int n = e / (KT / 8), k = (e % (KT / 8)) * 8;
+                const __nv_bfloat16* src = Mh + (size_t)(n0 + n) * m_n + k0 + k;
+                if (m_vec && n0 + n < N && k0 + k + 8 <= K) {
+                    *reinterpret_cast<uint4*>(&ms[n][k]) = *reinterpret_cast<const uint4*>(src);
+                } else {
+                    for (int j = 0; j < 8; ++j) ms[n][k + j] = (n0 + n < N && k0 + k + j < K) ? src[j] : zero;
+                }
+            } else {                                          // n contiguous (or neither): a piece is eight n of one k
+                const int k = e / 8, n = (e % 8) * 8;
+                const __nv_bfloat16* src = Mh + (size_t)(k0 + k) * m_k + (size_t)(n0 + n) * m_n;
+                if (m_vec && m_n == 1 && k0 + k < K && n0 + n + 8 <= N) {
+                    const uint4 w = *reinterpret_cast<const uint4*>(src);
+                    const __nv_bfloat16* wv = reinterpret_cast<const __nv_bfloat16*>(&w);
+                    for (int j = 0; j < 8; ++j) ms[n + j][k] = wv[j];
+                } else {
+                    for (int j = 0; j < 8; ++j) ms[n + j][k] = (k0 + k < K && n0 + n + j < N) ? src[(size_t)j * m_n] : zero;
+                }
+            }
         }
         __syncthreads();
 #pragma unroll
-        for (int kk = 0; kk < 32; kk += 16) {
+        for (int kk = 0; kk < KT; kk += 16) {
             uint32_t a0, a1, a2, a3;
-            fa::ldmatrix_x4(xs_a + (uint32_t)(((warp * 16 + (lane & 15)) * 40 + kk + (lane >> 4) * 8) * 2), a0, a1, a2, a3);
+            fa::ldmatrix_x4(xs_a + (uint32_t)(((warp * 16 + (lane & 15)) * LD + kk + (lane >> 4) * 8) * 2), a0, a1, a2, a3);
 #pragma unroll
             for (int n = 0; n < 8; n += 2) {
                 uint32_t b0, b1, b2, b3;
-                fa::ldmatrix_x4(ms_a + (uint32_t)(((n * 8 + ((lane >> 4) << 3) + (lane & 7)) * 40 + kk + ((lane >> 3) & 1) * 8) * 2),
+                fa::ldmatrix_x4(ms_a + (uint32_t)(((n * 8 + ((lane >> 4) << 3) + (lane & 7)) * LD + kk + ((lane >> 3) & 1) * 8) * 2),
                                 b0, b1, b2, b3);
                 fa::mma_16816(acc[n], a0, a1, a2, a3, b0, b1);
                 fa::mma_16816(acc[n + 1], a0, a1, a2, a3, b2, b3);
@@ -294,7 +332,7 @@ extern "C" int citlali_heads_product(const void* x, int x_dtype, size_t x_row, i
         set_last_error("heads_product: %d rotated dimensions of a tail of %d", rot_dims, tail);
         return kBadShape;
     }
-    if (m_dtype == kBF16 && rows >= 16) {                    // enough rows to fill MMA tiles
+    if (m_dtype == kBF16) {
         dim3 grid((rows + 63) / 64, heads, (N + 63) / 64);
         return CITLALI_DISPATCH_FLOAT(x_dtype, TX, [&] {
             return CITLALI_DISPATCH_FLOAT(y_dtype, TY, [&] {

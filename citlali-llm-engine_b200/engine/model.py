@@ -117,8 +117,7 @@ class DecoderModel:
             ops.embed_rows(self.embedding, batch.tokens, x, ctx.error_flag, emb_scale)
         else:                       # every stream starts as the embedding's rows
             x = torch.empty((streams, batch.rows, spec.hidden_size), dtype=torch.float32, device=ctx.device)
-            for s in range(streams):
-                ops.embed_rows(self.embedding, batch.tokens, x[s], ctx.error_flag, emb_scale)
+            ops.embed_rows_streams(self.embedding, batch.tokens, x, ctx.error_flag, emb_scale)
         batch.norm_carry = None
         batch.stream_write = None
         for i, step in enumerate(spec.schedule):

@@ -94,6 +94,19 @@ def embed_rows(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err
                                     _i(hidden), _i(table.shape[0]), _f(scale), _ptr(error_flag), _stream()), "embed_rows")
 
 
+def embed_rows_streams(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, error_flag: torch.Tensor,
+                       scale: float = 1.0):
+    """``out[s] = table[tokens] * scale`` for every stream s of ``out`` [streams, rows, hidden], in one launch."""
+    _need_cuda(table, tokens, out, error_flag)
+    require(tokens.dtype == torch.int32 and out.dtype == torch.float32 and out.dim() == 3,
+            "embed_rows_streams: tokens int32, out float32 [streams, rows, hidden]")
+    streams, rows, hidden = out.shape
+    require(table.shape[1] == hidden and tokens.numel() == rows, "embed_rows_streams: shapes do not fit")
+    _check(lib().citlali_embed_rows_copies(_ptr(table), _i(_dtype_code(table)), _ptr(tokens), _ptr(out), _i(rows),
+                                           _i(hidden), _i(table.shape[0]), _f(scale), _ptr(error_flag), _i(streams),
+                                           ctypes.c_size_t(rows * hidden), _stream()), "embed_rows")
+
+
 def scale_(x: torch.Tensor, scale: float):
     """x *= scale in place (float32)."""
     _need_cuda(x)

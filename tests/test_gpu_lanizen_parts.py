@@ -353,7 +353,7 @@ def test_walk_sink_takes_weight_without_a_value():
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_heads_product_both_orientations(dtype):
     rows, H, K, N, tail = 11, 3, 20, 70, 6
-    x = torch.randn(rows, H * (K + tail))
+    x = torch.randn(rows, H * (K + tail)).to(torch.bfloat16).float()      # the tensor-core form rounds x to bfloat16
     M = torch.randn(H * K, N).to(torch.bfloat16).float()                      # [h, k, n] as stored
     inv = torch.tensor([1.0, 0.1], dtype=torch.float32)
     pos = torch.arange(100, 100 + rows, dtype=torch.int32)
@@ -367,7 +367,7 @@ def test_heads_product_both_orientations(dtype):
     Mt = torch.randn(H * N, K).to(torch.bfloat16).float()                     # [h, n, k] as stored: y = x . M_h^T
     gate = torch.randn(rows, 5 + H * N)
     out = torch.empty(rows, H * N, dtype=dtype, device=DEV)
-    x2 = torch.randn(rows, H * K)
+    x2 = torch.randn(rows, H * K).to(torch.bfloat16).float()
     gd = gate.to(DEV)
     ops.heads_product(x2.to(DEV), H * K, K, Mt.to(DEV, dtype), N * K, 1, K, out, H * N, N, rows, H, K, N,
                       gate=gd[:, 5:], gate_stride=gd.shape[1])
