@@ -12,7 +12,7 @@
 //                   for q and k heads, beta = sigmoid(.), g = exp(-exp(A_log) softplus(. + dt_bias)).  All float32.
 //                   A second launch then moves the sequence's last taps-1 inputs into its state.
 //   delta_rule      one warp a (sequence, head, 8 columns), four lanes a column: the recurrence.
-//   delta_output    one block a row: each head's output divided by its root mean square, times a weight, times
+//   delta_output    one warp a (row, head): each head's output divided by its root mean square, times a weight, times
 //                   SiLU(gate); rounded once to the compute dtype.
 #include "api.h"
 #include "common.cuh"
@@ -211,7 +211,7 @@ delta_output_kernel(const float* __restrict__ o, const float* __restrict__ gate,
     dependents_may_launch();
     wait_for_predecessor();
     const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    for (int h = warp; h < H; h += warps) {
+    for (int h = blockIdx.y * warps + warp; h < H; h += gridDim.y * warps) {
         const float* src = o + ((size_t)row * H + h) * V;
         float ss = 0.0f;
         for (int i = lane; i < V; i += 32) ss = fmaf(src[i], src[i], ss);
@@ -285,7 +285,8 @@ extern "C" int citlali_delta_output(const float* o, const float* gate, int gate_
                                     int y_dtype, int rows, int H, int V, float eps, cudaStream_t stream) {
     if (rows <= 0) return 0;
     return CITLALI_DISPATCH_FLOAT(y_dtype, TO, [&] {
-        launch_kernel(delta_output_kernel<TO>, rows, 256, 0, stream, o, gate, gate_stride, weight, (TO*)y, H, V, eps);
+        dim3 grid(rows, (H + 7) / 8 < 64 ? (H + 7) / 8 : 64);             // a warp a head, eight heads a block
+        launch_kernel(delta_output_kernel<TO>, grid, 256, 0, stream, o, gate, gate_stride, weight, (TO*)y, H, V, eps);
         return CITLALI_LAUNCH_CHECK();
     });
 }

@@ -128,7 +128,7 @@ __global__ void stream_sum_kernel(const float* __restrict__ X, size_t stream_str
     dependents_may_launch();
     wait_for_predecessor();
     const size_t src = (size_t)(index ? index[blockIdx.x] : blockIdx.x) * W;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < W; i += gridDim.y * blockDim.x) {
         float v = 0.0f;
         for (int s = 0; s < S; ++s) v += X[s * stream_stride + src + i];
         out[(size_t)blockIdx.x * W + i] = v;
@@ -205,7 +205,8 @@ extern "C" int citlali_hyper_write_read_norm(float* X, size_t stream_stride, int
 extern "C" int citlali_stream_sum(const float* X, size_t stream_stride, int streams, const int32_t* index, float* out,
                                   int rows, int width, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    launch_kernel(stream_sum_kernel, rows, 256, 0, stream, X, stream_stride, streams, index, out, width);
+    dim3 grid(rows, rows < 64 ? (width + 255) / 256 : 1);          // few rows: a row's columns over several blocks
+    launch_kernel(stream_sum_kernel, grid, 256, 0, stream, X, stream_stride, streams, index, out, width);
     return CITLALI_LAUNCH_CHECK();
 }
 
