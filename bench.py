@@ -319,7 +319,7 @@ class ClockSampler:
 
 def run_design(args):
     """``--design``: a design beside the Qwen3 decoder at equal width, depth and parameter count (see
-    ``citlali_b200.measure``).  One JSON line; the default workload's line and contract are not touched."""
+    ``citlali_b200.measure``).  One JSON line; the default workload and its line are not touched."""
     import citlali_b200  # noqa: F401  (loads the package under its importable name)
     from citlali_b200 import measure
     sizes = [s for s in args.sizes.split(",") if s]
