@@ -153,7 +153,7 @@ def print_model_info(model_path: str, out=sys.stdout) -> None:
     kv = state = 0
     for req in cache_requirements_of(spec):
         if isinstance(req, KVRequirement):
-            kv += 2 * req.num_kv_heads * req.head_dim
+            kv += req.num_kv_heads * (req.head_dim + (req.head_dim if req.value_dim is None else req.value_dim))
         elif isinstance(req, StateRequirement):
             n = torch_element_size(req.dtype)
             for s in req.shape:

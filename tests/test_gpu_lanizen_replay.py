@@ -4,6 +4,11 @@ whole prompts; prompts with their tails decoded token by token; every token alon
 join a running batch; long decoding past every window and over several pages; bin/trace_run; greedy generation
 through ``generate`` (whose decode steps are replayed CUDA graphs).  In 32-bit the ways of cutting a sequence must
 agree to rounding with the exact evaluation; in bfloat16 within the rounding of 8-bit mantissas."""
+import json
+import os
+import subprocess
+import sys
+
 import pytest
 import torch
 
@@ -135,3 +140,21 @@ def test_greedy_generation_follows_plain(models, name, graphs):
                 assert int(row.argmax()) == tok, f"{name}: token {i} of a prompt of {len(prompt)}"
                 compared += 1
     assert compared >= 100
+
+
+def test_command_line(models):
+    """bin/citlali_cli on a Lanizen folder: the same tokens as ``generate``, and --info from the configuration alone."""
+    cli = os.path.join(replay.ROOT, "bin", "citlali_cli")
+    path = models["R"][0]
+    out = subprocess.run([sys.executable, cli, "--model", path, "--prompt-ids", "1,2,3,4,5", "--prompt-ids", "9,8,7",
+                          "--max-new-tokens", "6", "--ctx", "64", "--dtype", "float32", "--json"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    data = json.loads(out.stdout)
+    session = cb.InferenceSession().load_model(path, max_context=64, dtype="float32", max_batch=8)
+    want = session.generate([[1, 2, 3, 4, 5], [9, 8, 7]], cb.GenerationOptions(max_new_tokens=6, max_context=64))
+    assert [r["tokens"] for r in data["results"]] == [r.tokens for r in want]
+    info = subprocess.run([sys.executable, cli, "--model", path, "--info"], capture_output=True, text=True, timeout=120)
+    assert info.returncode == 0 and "architecture: Lanizen" in info.stdout and "streams: 4" in info.stdout
+    assert "cache bytes per token (bfloat16): %d" % (2 * (96 + 32) + 2 * (12 + 4)) in info.stdout
+    assert "state bytes per sequence: %d" % (4 * (8 * 80 * 40 + 3 * (2 * 2 * 80 + 8 * 40))) in info.stdout
