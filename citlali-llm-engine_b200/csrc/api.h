@@ -182,8 +182,9 @@ int citlali_delta_prepare(const float* proj, int proj_stride, const float* taps_
                           const int32_t* seq_slot, int sequences, const float* a_log, const float* dt_bias, float* prep,
                           int rows, int H, int KH, int D, int V, float unit_eps, cudaStream_t stream);
 // The recurrence over each sequence's rows, from and into state[slot][0 ...] = S [H, D, V]; out [rows, H V] float32.
+// pairs != 0: a sequence's rows are taken two at a time (the same numbers up to rounding, fewer dependent steps).
 int citlali_delta_rule(const float* prep, int prep_stride, float* state, size_t state_stride, const int32_t* seq_start,
-                       const int32_t* seq_slot, int sequences, int H, int KH, int D, int V, float* out,
+                       const int32_t* seq_slot, int sequences, int H, int KH, int D, int V, float* out, int pairs,
                        cudaStream_t stream);
 // y[r, h, :] = o[r, h, :] / sqrt(mean(o^2) + eps) * weight * silu(gate[r * gate_stride + h V ...]).
 int citlali_delta_output(const float* o, const float* gate, int gate_stride, const float* weight, void* y, int y_dtype,

@@ -106,7 +106,7 @@ template <int DP>
 __global__ void __launch_bounds__(128)
 delta_rule_kernel(const float* __restrict__ prep, int prep_stride, float* __restrict__ state, size_t state_stride,
                   const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot, int sequences,
-                  int H, int KH, int D, int V, float* __restrict__ out) {
+                  int H, int KH, int D, int V, float* __restrict__ out, int pairs) {
     constexpr int STAGES = DP <= 128 ? 8 : 4;    // tokens in flight from global memory: a warp is alone with their latency
     constexpr int STRIDE = 2 * DP + 16;          // floats a token takes in the ring: k | q | v of 8 columns | beta | g
     __shared__ __align__(16) float ring[4][STAGES][STRIDE];
@@ -157,7 +157,84 @@ delta_rule_kernel(const float* __restrict__ prep, int prep_stride, float* __rest
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     for (int s = 0; s < STAGES - 1; ++s) issue(r0 + s);
-    for (int row = r0; row < r1; ++row) {
+    int row = r0;
+    if (pairs) {
+        // Two tokens at a time.  With S the state before both, every sum over the rows of S is taken against S itself,
+        //   a1 = S^T k1, a2 = S^T k2, b1 = S^T q1, b2 = S^T q2   (four independent chains over the lane's rows),
+        // and the rest are scalars of the head (k1.k2, q1.k1, q2.k1, q2.k2) and of the column:
+        //   u1 = beta1 (v1 - g1 a1);            o1 = g1 b1 + u1 (q1.k1)
+        //   u2 = beta2 (v2 - g2 (g1 a2 + u1 (k1.k2)));   o2 = g2 (g1 b2 + u1 (q2.k1)) + u2 (q2.k2)
+        //   S <- g2 g1 S + k1 (g2 u1) + k2 u2.
+        // The same numbers as two single steps up to rounding; half the dependent steps a token.
+        for (; row + 1 < r1; row += 2) {
+            asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 3) : "memory");
+            __syncwarp();
+            issue(row + STAGES - 1);                      // into the place of the row before this pair
+            const float* c1 = ring[warp][(row - r0) % STAGES];
+            const float* c2 = ring[warp][(row + 1 - r0) % STAGES];
+            float kk = 0.0f, q1k1 = 0.0f, q2k1 = 0.0f, q2k2 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) {
+                const int i = j * 32 + lane;
+                const float a = c1[i], b = c2[i], c = c1[DP + i], d = c2[DP + i];
+                kk = fmaf(a, b, kk); q1k1 = fmaf(c, a, q1k1); q2k1 = fmaf(d, a, q2k1); q2k2 = fmaf(d, b, q2k2);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                kk += __shfl_xor_sync(0xffffffffu, kk, o);
+                q1k1 += __shfl_xor_sync(0xffffffffu, q1k1, o);
+                q2k1 += __shfl_xor_sync(0xffffffffu, q2k1, o);
+                q2k2 += __shfl_xor_sync(0xffffffffu, q2k2, o);
+            }
+            const float v1 = c1[2 * DP + (lane >> 2)], beta1 = c1[2 * DP + 8], g1 = c1[2 * DP + 9];
+            const float v2 = c2[2 * DP + (lane >> 2)], beta2 = c2[2 * DP + 8], g2 = c2[2 * DP + 9];
+            float a1x = 0.f, a1y = 0.f, a2x = 0.f, a2y = 0.f, b1x = 0.f, b1y = 0.f, b2x = 0.f, b2y = 0.f;
+            float4 k1r[GROUPS], k2r[GROUPS];
+#pragma unroll
+            for (int j = 0; j < GROUPS; ++j) {
+                const int at = (4 * j + part) * 4;
+                k1r[j] = *reinterpret_cast<const float4*>(c1 + at);
+                k2r[j] = *reinterpret_cast<const float4*>(c2 + at);
+                const float4 q1 = *reinterpret_cast<const float4*>(c1 + DP + at);
+                const float4 q2 = *reinterpret_cast<const float4*>(c2 + DP + at);
+                a1x = fmaf(S[j][0], k1r[j].x, a1x); a1y = fmaf(S[j][1], k1r[j].y, a1y);
+                a1x = fmaf(S[j][2], k1r[j].z, a1x); a1y = fmaf(S[j][3], k1r[j].w, a1y);
+                a2x = fmaf(S[j][0], k2r[j].x, a2x); a2y = fmaf(S[j][1], k2r[j].y, a2y);
+                a2x = fmaf(S[j][2], k2r[j].z, a2x); a2y = fmaf(S[j][3], k2r[j].w, a2y);
+                b1x = fmaf(S[j][0], q1.x, b1x); b1y = fmaf(S[j][1], q1.y, b1y);
+                b1x = fmaf(S[j][2], q1.z, b1x); b1y = fmaf(S[j][3], q1.w, b1y);
+                b2x = fmaf(S[j][0], q2.x, b2x); b2y = fmaf(S[j][1], q2.y, b2y);
+                b2x = fmaf(S[j][2], q2.z, b2x); b2y = fmaf(S[j][3], q2.w, b2y);
+            }
+            float a1 = a1x + a1y, a2 = a2x + a2y, b1 = b1x + b1y, b2 = b2x + b2y;
+#pragma unroll
+            for (int o = 1; o <= 2; o <<= 1) {
+                a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+                a2 += __shfl_xor_sync(0xffffffffu, a2, o);
+                b1 += __shfl_xor_sync(0xffffffffu, b1, o);
+                b2 += __shfl_xor_sync(0xffffffffu, b2, o);
+            }
+            const float u1 = beta1 * (v1 - g1 * a1);
+            const float o1 = fmaf(u1, q1k1, g1 * b1);
+            const float u2 = beta2 * (v2 - g2 * fmaf(u1, kk, g1 * a2));
+            const float o2 = fmaf(u2, q2k2, g2 * fmaf(u1, q2k1, g1 * b2));
+            const float gg = g1 * g2, w1 = g2 * u1;
+#pragma unroll
+            for (int j = 0; j < GROUPS; ++j) {
+                S[j][0] = fmaf(k2r[j].x, u2, fmaf(k1r[j].x, w1, gg * S[j][0]));
+                S[j][1] = fmaf(k2r[j].y, u2, fmaf(k1r[j].y, w1, gg * S[j][1]));
+                S[j][2] = fmaf(k2r[j].z, u2, fmaf(k1r[j].z, w1, gg * S[j][2]));
+                S[j][3] = fmaf(k2r[j].w, u2, fmaf(k1r[j].w, w1, gg * S[j][3]));
+            }
+            if (live && part == 0) {
+                out[(size_t)row * H * V + head * V + col] = o1;
+                out[(size_t)(row + 1) * H * V + head * V + col] = o2;
+            }
+            __syncwarp();                                 // both rows' places are read for the last time
+            issue(row + STAGES);
+        }
+    }
+    for (; row < r1; ++row) {
         asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
         __syncwarp();                            // this row's inputs are visible; the row before is no longer read
         issue(row + STAGES - 1);
@@ -256,7 +333,7 @@ extern "C" int citlali_delta_prepare(const float* proj, int proj_stride, const f
 
 extern "C" int citlali_delta_rule(const float* prep, int prep_stride, float* state, size_t state_stride,
                                   const int32_t* seq_start, const int32_t* seq_slot, int sequences, int H, int KH, int D,
-                                  int V, float* out, cudaStream_t stream) {
+                                  int V, float* out, int pairs, cudaStream_t stream) {
     if (sequences <= 0) return 0;
     if (D > 256) {
         set_last_error("delta_rule: a head size of %d exceeds 256", D);
@@ -266,7 +343,7 @@ extern "C" int citlali_delta_rule(const float* prep, int prep_stride, float* sta
     const int blocks = (int)((units + 3) / 4);
 #define CITLALI_DELTA(DP)                                                                                         \
     launch_kernel(delta_rule_kernel<DP>, blocks, 128, 0, stream, prep, prep_stride, state, state_stride, seq_start, \
-                  seq_slot, sequences, H, KH, D, V, out)
+                  seq_slot, sequences, H, KH, D, V, out, pairs)
     switch ((D + 31) / 32) {
         case 1: CITLALI_DELTA(32); break;
         case 2: CITLALI_DELTA(64); break;

@@ -527,13 +527,13 @@ def delta_prepare(proj, taps_w, state, conv_off, row_slot, seq_start, seq_slot, 
 _KERNELS_PER_CALL["delta_prepare_kept"] = 2
 
 
-def delta_rule(prep, state, seq_start, seq_slot, sequences, H, KH, D, V, out):
+def delta_rule(prep, state, seq_start, seq_slot, sequences, H, KH, D, V, out, pairs=False):
     _need_cuda(prep, state, seq_start, seq_slot, out)
     require(prep.dtype == torch.float32 and state.dtype == torch.float32 and out.dtype == torch.float32
             and out.shape == (prep.shape[0], H * V) and state.shape[1] >= H * D * V, "delta_rule: shapes or dtypes do not fit")
     _check(lib().citlali_delta_rule(_ptr(prep), _i(prep.shape[1]), _ptr(state), _sz(state.shape[1]), _ptr(seq_start),
-                                    _ptr(seq_slot), _i(sequences), _i(H), _i(KH), _i(D), _i(V), _ptr(out), _stream()),
-           "delta_rule")
+                                    _ptr(seq_slot), _i(sequences), _i(H), _i(KH), _i(D), _i(V), _ptr(out),
+                                    _i(1 if pairs else 0), _stream()), "delta_rule")
 
 
 def delta_output(o, gate, gate_stride, weight, y, H, V, eps):

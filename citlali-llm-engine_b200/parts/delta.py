@@ -101,7 +101,9 @@ class GatedDeltaMixer:
                           batch.seq_slot, batch.sequences, self.a_log, self.dt_bias, prep, self.H, self.KH, self.D,
                           self.V, _UNIT_EPS)
         o = torch.empty((rows, hv), dtype=torch.float32, device=proj.device)
-        ops.delta_rule(prep, state, batch.seq_start, batch.seq_slot, batch.sequences, self.H, self.KH, self.D, self.V, o)
+        # bfloat16 steps take a sequence's rows two at a time; the 32-bit path keeps one order of operations for every cut
+        ops.delta_rule(prep, state, batch.seq_start, batch.seq_slot, batch.sequences, self.H, self.KH, self.D, self.V, o,
+                       pairs=self.dtype == torch.bfloat16)
         y = torch.empty((rows, hv), dtype=self.dtype, device=proj.device)
         ops.delta_output(o, proj[:, self.C:], proj.shape[1], self.norm_w, y, self.H, self.V, self.eps)
         if overwrite:

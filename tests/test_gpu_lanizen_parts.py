@@ -446,3 +446,42 @@ def test_tensor_core_walk_in_runs(splits):
                              torch.tensor(positions, dtype=torch.int32, device=DEV), sink.to(DEV), out, H, R, E, 64, window,
                              0.1, splits=splits)
         close(out, _walk_plain(q, keys, positions, sink, H, R, E, window, 0.1), torch.bfloat16, bf16=1e-2)
+
+
+@pytest.mark.parametrize("D, V", [(32, 40), (128, 24), (80, 8)])
+def test_delta_rule_two_tokens_at_a_time(D, V):
+    """The form that takes a sequence's rows in pairs against the plain recurrence: even and odd lengths, a single row,
+    three sequences in one launch, states carried over from a launch before."""
+    H, KH = 4, 2
+    C = 2 * KH * D + H * V
+    lengths = [7, 1, 64]
+    T = sum(lengths)
+    g = torch.Generator().manual_seed(D + V)
+    prep = torch.zeros(T, C + 2 * H)
+    prep[:, :2 * KH * D] = torch.nn.functional.normalize(torch.randn(T, 2 * KH, D, generator=g), dim=-1).view(T, -1)
+    prep[:, :KH * D] *= D ** -0.5
+    prep[:, 2 * KH * D:C] = torch.randn(T, H * V, generator=g)
+    prep[:, C:C + H] = torch.rand(T, H, generator=g)
+    prep[:, C + H:] = 0.9 + 0.1 * torch.rand(T, H, generator=g)
+    seq_start = torch.tensor([0, 7, 8, T], dtype=torch.int32, device=DEV)
+    seq_slot = torch.tensor([2, 0, 1], dtype=torch.int32, device=DEV)
+    outs = {}
+    for pairs in (False, True):
+        state = torch.zeros(3, H * D * V, device=DEV)
+        out = torch.empty(T, H * V, device=DEV)
+        ops.delta_rule(prep.to(DEV), state, seq_start, seq_slot, 3, H, KH, D, V, out, pairs=pairs)
+        again = torch.empty(T, H * V, device=DEV)                # the same rows once more, from the states just left
+        ops.delta_rule(prep.to(DEV), state, seq_start, seq_slot, 3, H, KH, D, V, again, pairs=pairs)
+        outs[pairs] = (out.cpu(), again.cpu(), state.cpu())
+    for a, b in zip(outs[False], outs[True]):
+        assert torch.allclose(a, b, rtol=1e-4, atol=1e-5)
+    at = 0
+    for n in lengths:
+        for h in range(H):
+            kh = h // (H // KH)
+            rows = slice(at, at + n)
+            ref = plain.delta_rule(prep[rows, kh * D:(kh + 1) * D].double(), prep[rows, (KH + kh) * D:(KH + kh + 1) * D].double(),
+                                   prep[rows, 2 * KH * D + h * V:2 * KH * D + (h + 1) * V].double(),
+                                   prep[rows, C + H + h].double(), prep[rows, C + h].double())
+            close(outs[True][0][rows, h * V:(h + 1) * V], ref, torch.float32, f32=1e-4)
+        at += n
