@@ -176,11 +176,13 @@ int citlali_relu_squared(const void* x, void* y, int dtype, size_t n, cudaStream
 // q, k, v channels over time (taps_w [C, taps], the last column is the current token's; earlier tokens come from the
 // step's rows or from state[slot][conv_off ...], laid out [taps - 1, C]), applies SiLU, makes q and k heads unit
 // vectors (q also times D^-1/2), and writes prep [rows, C + 2 H] = q | k | v | sigmoid(b) | exp(-exp(a_log) softplus(a +
-// dt_bias)).  Then stores each sequence's last taps - 1 inputs in its state.
+// dt_bias)).  Then stores each sequence's last taps - 1 inputs in its state.  block_a_segment != 0: the form for steps of few
+// rows (a block a head instead of a warp; a head's squares are summed in another order, so a caller that wants the same bits
+// from every step size keeps to one form).
 int citlali_delta_prepare(const float* proj, int proj_stride, const float* taps_w, int taps, float* state,
                           size_t state_stride, size_t conv_off, const int32_t* row_slot, const int32_t* seq_start,
                           const int32_t* seq_slot, int sequences, const float* a_log, const float* dt_bias, float* prep,
-                          int rows, int H, int KH, int D, int V, float unit_eps, cudaStream_t stream);
+                          int rows, int H, int KH, int D, int V, float unit_eps, int block_a_segment, cudaStream_t stream);
 // The recurrence over each sequence's rows, from and into state[slot][0 ...] = S [H, D, V]; out [rows, H V] float32.
 // pairs != 0: a sequence's rows are taken two at a time (the same numbers up to rounding, fewer dependent steps).
 int citlali_delta_rule(const float* prep, int prep_stride, float* state, size_t state_stride, const int32_t* seq_start,

@@ -7,7 +7,7 @@
 // state and the outputs do not depend on how a sequence was cut into steps.
 //
 // Three kernels:
-//   delta_prepare   one block a (row, q head / k head / head's values): the short causal convolution over time of the q, k, v channels (earlier tokens
+//   delta_prepare   one warp a (row, q head / k head / head's values): the short causal convolution over time of the q, k, v channels (earlier tokens
 //                   from the step's rows or, before its first row, from the sequence's kept inputs), SiLU, unit length
 //                   for q and k heads, beta = sigmoid(.), g = exp(-exp(A_log) softplus(. + dt_bias)).  All float32.
 //                   A second launch then moves the sequence's last taps-1 inputs into its state.
@@ -29,8 +29,76 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
 // proj [rows, proj_stride] float32 holds, per row: q (KH*D) | k (KH*D) | v (H*V) | gate (H*V) | b (H) | a (H).
 // prep [rows, C + 2H] receives q^ | k^ | v | beta | g, C = 2 KH D + H V.
 // conv_state [slot] is [taps-1, C]: the inputs at the sequence's last taps-1 positions, oldest first.
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 delta_prepare_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ taps_w, int taps,
+                     const float* __restrict__ state, size_t state_stride, size_t conv_off,
+                     const int32_t* __restrict__ row_slot, const float* __restrict__ a_log,
+                     const float* __restrict__ dt_bias, float* __restrict__ prep, int H, int KH, int D, int V, float unit_eps) {
+    dependents_may_launch();
+    wait_for_predecessor();
+    // A warp: one row and one segment of its channels (a q head, a k head, or a head's values); eight segments a block.
+    const int row = blockIdx.x, lane = threadIdx.x & 31;
+    const int seg = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int C = 2 * KH * D + H * V;
+    float* dst = prep + (size_t)row * (C + 2 * H);
+    if (blockIdx.y == 0 && threadIdx.x < H) {                 // the head's write strength and decay
+        const float* rest = proj + (size_t)row * proj_stride + C + H * V;
+        for (int h = threadIdx.x; h < H; h += blockDim.x) {
+            dst[C + h] = sigmoidf_(rest[h]);
+            dst[C + H + h] = expf(-expf(a_log[h]) * softplusf_(rest[H + h] + dt_bias[h]));
+        }
+    }
+    if (seg >= 2 * KH + H) return;
+    const bool unit = seg < 2 * KH;                           // q and k heads are made unit vectors
+    const int c0 = unit ? seg * D : 2 * KH * D + (seg - 2 * KH) * V, n = unit ? D : V;
+    const int slot = row_slot[row];
+    int in_step = 0;                        // how many of the tokens before this one are rows of this step
+    while (in_step < taps - 1 && row - in_step - 1 >= 0 && row_slot[row - in_step - 1] == slot) ++in_step;
+    const float* kept = state + (size_t)slot * state_stride + conv_off;
+    auto convolved = [&](int i) {
+        const int c = c0 + i;
+        float acc = 0.0f;
+        for (int back = taps - 1; back >= 0; --back) {        // `back` tokens back; oldest first
+            float x;
+            if (back <= in_step) x = proj[(size_t)(row - back) * proj_stride + c];
+            else x = kept[(size_t)(taps - 1 - back + in_step) * C + c];
+            acc = fmaf(taps_w[(size_t)c * taps + (taps - 1 - back)], x, acc);
+        }
+        return siluf_(acc);
+    };
+    // a lane's channels are lane, lane + 32, ...: the first eight stay in registers between the two passes, a longer
+    // segment parks the rest in the output row
+    float keep[8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = lane + 32 * j;
+        keep[j] = i < n ? convolved(i) : 0.0f;
+        ss = fmaf(keep[j], keep[j], ss);
+    }
+    for (int i = lane + 256; i < n; i += 32) {
+        const float v = convolved(i);
+        dst[c0 + i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    float f = 1.0f;
+    if (unit) {
+        ss = warp_sum(ss);
+        f = 1.0f / sqrtf(ss + unit_eps);
+        if (seg < KH) f /= sqrtf((float)D);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = lane + 32 * j;
+        if (i < n) dst[c0 + i] = keep[j] * f;
+    }
+    for (int i = lane + 256; i < n; i += 32) dst[c0 + i] *= f;
+}
+
+// The same with a block of 128 threads a segment, a thread a channel: for steps of few rows, where a row's segments
+// are all the parallelism there is.  (It sums a head's squares in another order than the kernel above.)
+__global__ void __launch_bounds__(128)
+delta_prepare_block_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ taps_w, int taps,
                      const float* __restrict__ state, size_t state_stride, size_t conv_off,
                      const int32_t* __restrict__ row_slot, const float* __restrict__ a_log,
                      const float* __restrict__ dt_bias, float* __restrict__ prep, int H, int KH, int D, int V, float unit_eps) {
@@ -308,21 +376,32 @@ extern "C" int citlali_delta_prepare(const float* proj, int proj_stride, const f
                                      size_t state_stride, size_t conv_off, const int32_t* row_slot,
                                      const int32_t* seq_start, const int32_t* seq_slot, int sequences,
                                      const float* a_log, const float* dt_bias, float* prep, int rows, int H, int KH,
-                                     int D, int V, float unit_eps, cudaStream_t stream) {
+                                     int D, int V, float unit_eps, int block_a_segment, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (H <= 0 || KH <= 0 || H % KH != 0 || D <= 0 || V <= 0 || taps < 1) {
         set_last_error("delta_prepare: %d heads over %d key heads of %d, values of %d, %d taps", H, KH, D, V, taps);
         return kBadShape;
     }
     const int C = 2 * KH * D + H * V;
-    const size_t smem = (size_t)(D > V ? D : V) * sizeof(float);
-    if (smem > 48 * 1024 || 2 * KH + H > 65535) {
-        set_last_error("delta_prepare: heads of %d and values of %d, or %d segments a row, are too many", D, V, 2 * KH + H);
+    const int segments = 2 * KH + H;
+    if ((segments + 7) / 8 > 65535) {
+        set_last_error("delta_prepare: %d segments a row are too many", segments);
         return kTooLarge;
     }
-    dim3 prepare_grid(rows, 2 * KH + H);
-    launch_kernel(delta_prepare_kernel, prepare_grid, 128, smem, stream, proj, proj_stride, taps_w, taps, (const float*)state,
-                  state_stride, conv_off, row_slot, a_log, dt_bias, prep, H, KH, D, V, unit_eps);
+    if (block_a_segment) {
+        const size_t smem = (size_t)(D > V ? D : V) * sizeof(float);
+        if (smem > 48 * 1024 || segments > 65535) {
+            set_last_error("delta_prepare: heads of %d and values of %d, or %d segments a row, are too many", D, V, segments);
+            return kTooLarge;
+        }
+        dim3 prepare_grid(rows, segments);
+        launch_kernel(delta_prepare_block_kernel, prepare_grid, 128, smem, stream, proj, proj_stride, taps_w, taps,
+                      (const float*)state, state_stride, conv_off, row_slot, a_log, dt_bias, prep, H, KH, D, V, unit_eps);
+    } else {
+        dim3 prepare_grid(rows, (segments + 7) / 8);
+        launch_kernel(delta_prepare_kernel, prepare_grid, 256, 0, stream, proj, proj_stride, taps_w, taps, (const float*)state,
+                      state_stride, conv_off, row_slot, a_log, dt_bias, prep, H, KH, D, V, unit_eps);
+    }
     int code = CITLALI_LAUNCH_CHECK();
     if (code != 0 || taps == 1) return code;
     dim3 grid(sequences, (C + 127) / 128);

@@ -139,7 +139,19 @@ template <typename T>
 __global__ void relu_squared_kernel(const T* x, T* y, size_t n) {
     dependents_may_launch();
     wait_for_predecessor();
-    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+    constexpr int PER = 16 / sizeof(T);                       // elements of a 16-byte access
+    const size_t pieces = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0 ? n / PER : 0;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < pieces; e += (size_t)gridDim.x * blockDim.x) {
+        uint4 w = reinterpret_cast<const uint4*>(x)[e];
+        T* v = reinterpret_cast<T*>(&w);
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const float f = fmaxf(ldf(v, j), 0.0f);
+            stf(v, j, f * f);
+        }
+        reinterpret_cast<uint4*>(y)[e] = w;
+    }
+    for (size_t e = pieces * PER + (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
         const float v = fmaxf(ldf(x, e), 0.0f);
         stf(y, e, v * v);
     }

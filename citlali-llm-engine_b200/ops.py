@@ -507,7 +507,7 @@ def relu_squared(x: torch.Tensor, y: torch.Tensor):
 # ---- the gated delta rule ------------------------------------------------------------------------
 
 def delta_prepare(proj, taps_w, state, conv_off, row_slot, seq_start, seq_slot, sequences, a_log, dt_bias, prep,
-                  H, KH, D, V, unit_eps):
+                  H, KH, D, V, unit_eps, block_a_segment=False):
     """See ``citlali_delta_prepare`` (csrc/api.h).  ``state`` [slots, n] float32; two launches unless taps == 1."""
     _need_cuda(proj, taps_w, state, row_slot, seq_start, seq_slot, a_log, dt_bias, prep)
     rows = proj.shape[0]
@@ -521,7 +521,8 @@ def delta_prepare(proj, taps_w, state, conv_off, row_slot, seq_start, seq_slot, 
     _check(lib().citlali_delta_prepare(_ptr(proj), _i(proj.shape[1]), _ptr(taps_w), _i(taps), _ptr(state),
                                        _sz(state.shape[1]), _sz(conv_off), _ptr(row_slot), _ptr(seq_start), _ptr(seq_slot),
                                        _i(sequences), _ptr(a_log), _ptr(dt_bias), _ptr(prep), _i(rows), _i(H), _i(KH),
-                                       _i(D), _i(V), _f(unit_eps), _stream()), "delta_prepare" if taps == 1 else "delta_prepare_kept")
+                                       _i(D), _i(V), _f(unit_eps), _i(1 if block_a_segment else 0), _stream()),
+           "delta_prepare" if taps == 1 else "delta_prepare_kept")
 
 
 _KERNELS_PER_CALL["delta_prepare_kept"] = 2

@@ -99,7 +99,7 @@ class GatedDeltaMixer:
         prep = torch.empty((rows, self.C + 2 * self.H), dtype=torch.float32, device=proj.device)
         ops.delta_prepare(proj, self.conv_w, state, self.H * self.D * self.V, batch.row_slot, batch.seq_start,
                           batch.seq_slot, batch.sequences, self.a_log, self.dt_bias, prep, self.H, self.KH, self.D,
-                          self.V, _UNIT_EPS)
+                          self.V, _UNIT_EPS, block_a_segment=self.dtype == torch.bfloat16 and rows < 64)
         o = torch.empty((rows, hv), dtype=torch.float32, device=proj.device)
         # bfloat16 steps take a sequence's rows two at a time; the 32-bit path keeps one order of operations for every cut
         ops.delta_rule(prep, state, batch.seq_start, batch.seq_slot, batch.sequences, self.H, self.KH, self.D, self.V, o,
