@@ -118,6 +118,20 @@ def test_trace_run_program(models, dtype):
     check(got, plain_rows(models, name), dtype, f"trace_run {dtype}")
 
 
+def test_trace_run_counts_tokens_without_page_padding(models):
+    """--max-tokens is the number of tokens live requests hold, not whole pages: twelve requests of 1 to 12 tokens live
+    at once need twelve pages although they hold 78 tokens."""
+    name = "S"
+    _, cfg, w = models[name]
+    reqs = [(f"q{i}", random_tokens(CONFIGS[name]["vocab"], i + 1, 900 + i)) for i in range(12)]
+    steps = [{"step": 0, "entries": [{"id": rid, "tokens": toks, "want": [len(toks) - 1]} for rid, toks in reqs],
+              "end": [rid for rid, _ in reqs]}]
+    got = replay.run_trace_run(models[name][0], "float32", steps, CONFIGS[name]["vocab"],
+                               max_tokens=sum(len(t) for _, t in reqs))
+    want = {rid: plain.forward(cfg, w, toks) for rid, toks in reqs}
+    check(got, want, "float32", "trace_run with many short requests")
+
+
 @pytest.mark.parametrize("graphs", [True, False])
 @pytest.mark.parametrize("name", ["P", "R"])
 def test_greedy_generation_follows_plain(models, name, graphs):
