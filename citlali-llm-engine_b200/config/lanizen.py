@@ -142,7 +142,7 @@ class LanizenConfig:
                 mp = f"{p}.mix"
                 parts["mixer"] = PartSpec("gated_delta", {
                     "hidden_size": self.width, "heads": m["heads"], "kv_heads": m.get("kv_heads") or m["heads"],
-                    "dim": m["dim"], "vdim": m["vdim"], "conv": m.get("conv") or 1, "norm_eps": self.norm_eps,
+                    "dim": m["dim"], "vdim": m["vdim"], "conv": m.get("conv"), "norm_eps": self.norm_eps,
                     "names": {"q": f"{mp}.q", "k": f"{mp}.k", "v": f"{mp}.v", "gate": f"{mp}.g", "b": f"{mp}.b",
                               "a": f"{mp}.a", "q_conv": f"{mp}.q.conv", "k_conv": f"{mp}.k.conv", "v_conv": f"{mp}.v.conv",
                               "a_log": f"{mp}.A_log", "dt_bias": f"{mp}.dt_bias", "norm": f"{mp}.norm", "o": f"{mp}.o"},

@@ -15,7 +15,7 @@ projections are one product whose result is kept in float32.
 What a sequence keeps between steps (one float32 region per slot, zero at its start): S for every head, then the
 last ``conv - 1`` inputs of the convolved channels.
 
-Parameters: hidden_size, heads, kv_heads, dim, vdim, conv, norm_eps; ``names``: the tensors' full names by role
+Parameters: hidden_size, heads, kv_heads, dim, vdim, conv (None: no convolution and no tap tensors), norm_eps; ``names``: the tensors' full names by role
 (q, k, v, gate, b, a, q_conv, k_conv, v_conv, a_log, dt_bias, norm, o).
 """
 from __future__ import annotations
@@ -50,6 +50,7 @@ class GatedDeltaMixer:
         self.KH = int(params.get("kv_heads") or self.H)
         self.D = int(params["dim"])
         self.V = int(params["vdim"])
+        self.has_conv = params.get("conv") is not None       # no taps given: the channels pass straight to SiLU, no tensors
         self.taps = int(params.get("conv") or 1)
         self.eps = float(params["norm_eps"])
         require(self.H % self.KH == 0, f"{prefix}: {self.H} heads are not a multiple of {self.KH} query/key heads")
@@ -69,10 +70,11 @@ class GatedDeltaMixer:
 
     def tensor_specs(self):
         nm, qk, hv = self.names, self.KH * self.D, self.H * self.V
-        return self.proj.tensor_specs() + self.o.tensor_specs() + [
-            TensorSpec(nm["q_conv"], (qk, self.taps), "state"), TensorSpec(nm["k_conv"], (qk, self.taps), "state"),
-            TensorSpec(nm["v_conv"], (hv, self.taps), "state"), TensorSpec(nm["a_log"], (self.H,), "state"),
-            TensorSpec(nm["dt_bias"], (self.H,), "state"), TensorSpec(nm["norm"], (self.V,), "gain")]
+        conv = [TensorSpec(nm["q_conv"], (qk, self.taps), "state"), TensorSpec(nm["k_conv"], (qk, self.taps), "state"),
+                TensorSpec(nm["v_conv"], (hv, self.taps), "state")] if self.has_conv else []
+        return self.proj.tensor_specs() + self.o.tensor_specs() + conv + [
+            TensorSpec(nm["a_log"], (self.H,), "state"), TensorSpec(nm["dt_bias"], (self.H,), "state"),
+            TensorSpec(nm["norm"], (self.V,), "gain")]
 
     def cache_requirement(self):
         return StateRequirement((self.state_floats,), torch.float32)
@@ -81,9 +83,12 @@ class GatedDeltaMixer:
         nm, qk, hv = self.names, self.KH * self.D, self.H * self.V
         self.proj.bind(weights, ctx)
         self.o.bind(weights, ctx)
-        self.conv_w = torch.cat([bind_float32(weights, nm["q_conv"], (qk, self.taps), ctx),
-                                 bind_float32(weights, nm["k_conv"], (qk, self.taps), ctx),
-                                 bind_float32(weights, nm["v_conv"], (hv, self.taps), ctx)], 0).contiguous()
+        if self.has_conv:
+            self.conv_w = torch.cat([bind_float32(weights, nm["q_conv"], (qk, self.taps), ctx),
+                                     bind_float32(weights, nm["k_conv"], (qk, self.taps), ctx),
+                                     bind_float32(weights, nm["v_conv"], (hv, self.taps), ctx)], 0).contiguous()
+        else:
+            self.conv_w = torch.ones((self.C, 1), dtype=torch.float32, device=ctx.device)
         self.a_log = bind_float32(weights, nm["a_log"], (self.H,), ctx)
         self.dt_bias = bind_float32(weights, nm["dt_bias"], (self.H,), ctx)
         self.norm_w = bind_float32(weights, nm["norm"], (self.V,), ctx)

@@ -17,8 +17,10 @@ import citlali_b200 as cb
 
 
 def _delta(heads, kv_heads, dim, vdim, conv, ff):
-    return {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv},
-            "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim}
+    if conv is not None:
+        m["conv"] = conv
+    return {"type": "delta", "mixer": m, "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
 
 
 def _latent(heads, dim, rot_dim, vdim, q_rank, kv_rank, window, ff, kv_from=None, rot_dims=None, base=1e4, scale=0.25):
@@ -54,7 +56,8 @@ CONFIGS = {
     # one stream that still passes its three mixtures
     "S": {"architecture": "Lanizen", "vocab": 128, "width": 32, "norm": {"eps": 1e-5}, "streams": 1, "layers": [
               _delta(1, 1, 8, 8, 2, 48),
-              _latent(1, 8, 2, 8, 8, 8, 4, 48, scale=0.5)]},
+              _latent(1, 8, 2, 8, 8, 8, 4, 48, scale=0.5),
+              _delta(2, 2, 8, 12, None, None)]},
 }
 
 

@@ -69,9 +69,11 @@ def delta_mixer(h, w, p, m, eps):
     """The gated delta-rule mixer.  ``w``: weights, ``p``: the layer's prefix with '.mix', ``m``: its sizes."""
     T = h.shape[0]
     H, KH, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = silu(causal_conv(h @ f64(w[p + ".q"]).T, w[p + ".q.conv"])).view(T, KH, D)
-    k = silu(causal_conv(h @ f64(w[p + ".k"]).T, w[p + ".k.conv"])).view(T, KH, D)
-    v = silu(causal_conv(h @ f64(w[p + ".v"]).T, w[p + ".v.conv"])).view(T, H, V)
+    def conv(x, name):                       # a mixer without taps has no convolution
+        return causal_conv(x, w[name]) if m.get("conv") is not None else x
+    q = silu(conv(h @ f64(w[p + ".q"]).T, p + ".q.conv")).view(T, KH, D)
+    k = silu(conv(h @ f64(w[p + ".k"]).T, p + ".k.conv")).view(T, KH, D)
+    v = silu(conv(h @ f64(w[p + ".v"]).T, p + ".v.conv")).view(T, H, V)
     q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
     k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
     beta = torch.sigmoid(h @ f64(w[p + ".b"]).T)                                   # [T, H]
