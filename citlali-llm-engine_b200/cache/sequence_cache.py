@@ -33,11 +33,13 @@ PAGE_SIZE = 64
 class KVRequirement:
     """What an attention-like mixer needs cached per token: keys and values of ``num_kv_heads``
     heads of ``head_dim``; ``window`` keys back at most (None: all of them).  ``value_dim``: the size of a value
-    (None: ``head_dim``; 0: the mixer keeps one vector per token and no values, and the group holds no value pool)."""
+    (None: ``head_dim``; 0: the mixer keeps one vector per token and no values, and the group holds no value pool).
+    ``keep_first``: so many first tokens of a sequence stay visible beside the window."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: Optional[int] = None
+    keep_first: int = 0        # with a window: the sequence's first tokens stay visible, so their pages are never given back
 
 
 @dataclass(frozen=True)
@@ -100,17 +102,32 @@ class SequenceCache:
         self.kv_groups: List[KVGroup] = []
         self.state_groups: List[StateGroup] = []
         self._where: Dict[int, Tuple[str, int, int]] = {}     # step -> (kind, group, layer in group)
-        by_kv: Dict[KVRequirement, List[int]] = {}
-        by_state: Dict[StateRequirement, List[int]] = {}
+        by_kv: Dict[KVRequirement, List[object]] = {}
+        by_state: Dict[StateRequirement, List[object]] = {}
+        self._nested: Dict[int, object] = {}                  # step -> the keys of its requirements, nested as they were given
+
+        def place(key, req):
+            """A requirement may be a tuple of requirements (a mixer made of several, each with a cache of its own);
+            tuples nest.  ``key`` names one leaf: (step, index, index, ...)."""
+            if req is None:
+                return None
+            if isinstance(req, (tuple, list)):
+                return tuple(place(key + (j,), r) for j, r in enumerate(req))
+            if isinstance(req, KVRequirement):
+                by_kv.setdefault(req, []).append(key)
+            elif isinstance(req, StateRequirement):
+                by_state.setdefault(req, []).append(key)
+            else:
+                raise CitlaliError(f"schedule step {key[0]} asks for a cache of unknown kind {type(req).__name__}")
+            return key
+
         for step, req in enumerate(requirements):
             if req is None:
                 continue
-            if isinstance(req, KVRequirement):
-                by_kv.setdefault(req, []).append(step)
-            elif isinstance(req, StateRequirement):
-                by_state.setdefault(req, []).append(step)
+            if isinstance(req, (tuple, list)):
+                self._nested[step] = place((step,), req)
             else:
-                raise CitlaliError(f"schedule step {step} asks for a cache of unknown kind {type(req).__name__}")
+                place(step, req)
         self._pin = self.device.type == "cuda"
         self._has_window = any(req.window is not None for req in by_kv)
         for req, steps in by_kv.items():
@@ -201,7 +218,8 @@ class SequenceCache:
             if w is None:
                 continue
             first_visible = max(0, new_length - w + 1) // self.page_size
-            gone = [i for i in g.held[slot] if i < first_visible]
+            kept_pages = (g.requirement.keep_first + self.page_size - 1) // self.page_size     # they hold the first tokens
+            gone = [i for i in g.held[slot] if kept_pages <= i < first_visible]
             if gone:
                 g.pages.free([g.held[slot].pop(i) for i in gone])
 
@@ -215,9 +233,22 @@ class SequenceCache:
         self.lengths[slot] = new_length
 
     # ---- what layers see ---------------------------------------------------------------
-    def view(self, step: int):
-        require(step in self._where, f"schedule step {step} keeps no cache")
-        kind, gi, j = self._where[step]
+    def view(self, step):
+        """What the mixer of schedule step ``step`` sees: a view, or views nested like the requirements it gave."""
+        if step in self._nested:
+            return self._views(self._nested[step])
+        return self._view_of(step)
+
+    def _views(self, keys):
+        if keys is None:
+            return None
+        if isinstance(keys, tuple) and (len(keys) == 0 or not isinstance(keys[0], int)):
+            return tuple(self._views(k) for k in keys)
+        return self._view_of(keys)
+
+    def _view_of(self, key):
+        require(key in self._where, f"schedule step {key} keeps no cache")
+        kind, gi, j = self._where[key]
         if kind == "kv":
             g = self.kv_groups[gi]
             return KVView(g.keys[j], g.values[j], g.table, self.page_size, g.requirement)
@@ -225,7 +256,7 @@ class SequenceCache:
         return StateView(g.storage[j], g.requirement)
 
     def has_view(self, step: int) -> bool:
-        return step in self._where
+        return step in self._where or step in self._nested
 
     def bytes(self) -> int:
         total = 0

@@ -50,5 +50,16 @@ def config_from_dict(d: Dict[str, Any]):
 
 
 def config_from_model_dir(model_dir: str):
+    """The configuration of a model folder.  A class whose design leaves some sizes to the shapes of the checkpoint's
+    tensors offers ``with_tensor_shapes({name: shape})``; it is then given the shapes the folder's weight files declare
+    (their headers are read, no values)."""
     from .qwen3 import read_config_json
-    return config_from_dict(read_config_json(model_dir))
+    config = config_from_dict(read_config_json(model_dir))
+    if callable(getattr(config, "with_tensor_shapes", None)):
+        from ..weights.loader import WeightLoader
+        loader = WeightLoader(model_dir)
+        try:
+            config = config.with_tensor_shapes({n: tuple(loader.stored_shape(n)) for n in loader.names()})
+        finally:
+            loader.close()
+    return config

@@ -182,15 +182,97 @@ int citlali_relu_squared(const void* x, void* y, int dtype, size_t n, cudaStream
 int citlali_delta_prepare(const float* proj, int proj_stride, const float* taps_w, int taps, float* state,
                           size_t state_stride, size_t conv_off, const int32_t* row_slot, const int32_t* seq_start,
                           const int32_t* seq_slot, int sequences, const float* a_log, const float* dt_bias, float* prep,
-                          int rows, int H, int KH, int D, int V, float unit_eps, int block_a_segment, cudaStream_t stream);
+                          int rows, int H, int KH, int D, int V, float unit_eps, int block_a_segment, int beta_col,
+                          int decay_col, const float* decay_in, int decay_stride, int channel_decay, cudaStream_t stream);
+// (beta_col, decay_col: the columns of b and a in a row of proj.  decay_in (rows decay_stride floats apart) given: the
+// decays' inputs come from there instead of proj.  channel_decay: one decay a head and key channel instead of one a head,
+// g = exp(-exp(a_log[h]) softplus(decay_in[h D + i] + dt_bias[h D + i])); prep is then [rows, C + H + H D].)
 // The recurrence over each sequence's rows, from and into state[slot][0 ...] = S [H, D, V]; out [rows, H V] float32.
 // pairs != 0: a sequence's rows are taken two at a time (the same numbers up to rounding, fewer dependent steps).
+// mode 0: one decay a head; 1: a decay a key channel (row i of S times g_i; prep as above); 2: no correction term,
+// u = beta v, which is a state-space recurrence S <- g S + beta k v^T, o = S^T q.
 int citlali_delta_rule(const float* prep, int prep_stride, float* state, size_t state_stride, const int32_t* seq_start,
-                       const int32_t* seq_slot, int sequences, int H, int KH, int D, int V, float* out, int pairs,
+                       const int32_t* seq_slot, int sequences, int H, int KH, int D, int V, float* out, int pairs, int mode,
                        cudaStream_t stream);
-// y[r, h, :] = o[r, h, :] / sqrt(mean(o^2) + eps) * weight * silu(gate[r * gate_stride + h V ...]).
+// y[r, h, :] = o[r, h, :] / sqrt(mean(o^2) + eps) * weight * act(gate[r * gate_stride + h V ...]); gate_act 0: SiLU, 1: sigmoid.
 int citlali_delta_output(const float* o, const float* gate, int gate_stride, const float* weight, void* y, int y_dtype,
-                         int rows, int H, int V, float eps, cudaStream_t stream);
+                         int rows, int H, int V, float eps, int gate_act, cudaStream_t stream);
+
+// ---- a norm on a sub-layer's output ------------------------------------------------------------------------------
+// x[r] += layer_norm(y[r]) * gain  (mean and variance of the row, variance = mean of squared deviations, no bias), float32;
+// emit (may be null) receives the updated rows in emit_dtype.
+int citlali_layer_norm_add(const float* y, const void* gain, int gain_dtype, float* x, void* emit, int emit_dtype, int rows,
+                           int hidden, float eps, cudaStream_t stream);
+// out[i] = layer_norm(x[index[i]]) * gain (index may be null: identity).
+int citlali_layer_norm_rows(const float* x, const void* gain, int gain_dtype, const int32_t* row_index, void* out,
+                            int out_dtype, int rows, int hidden, float eps, cudaStream_t stream);
+// out = x converted from float32.
+int citlali_cast_rows(const float* x, void* out, int out_dtype, size_t n, cudaStream_t stream);
+// out = a l + b r over n floats.
+int citlali_scaled_sum(float a, const float* l, float b, const float* r, float* out, size_t n, cudaStream_t stream);
+
+// ---- mixers with a state per sequence ------------------------------------------------------------------------------
+// out[row, c] = act(sum_j taps_w[c, j] u(t - taps + 1 + j) + bias[c]) for channels c < C, where u of a row of this step is
+// in[row, c] + in_bias[c] and u of an earlier token comes from state[slot][conv_off ...] = [taps - 1, C] (zero at a
+// sequence's start).  in_bias and bias may be null; act 0: none, 1: SiLU.  keep != 0: afterwards every sequence's last
+// taps - 1 inputs are stored in its state (citlali_conv_keep).
+int citlali_causal_conv(const float* in, int in_stride, const float* in_bias, const float* taps_w, int taps, const float* bias,
+                        int act, float* state, size_t state_stride, size_t conv_off, const int32_t* row_slot,
+                        const int32_t* seq_start, const int32_t* seq_slot, int sequences, float* out, int out_stride, int rows,
+                        int C, int keep, cudaStream_t stream);
+int citlali_conv_keep(const float* in, int in_stride, const float* in_bias, int taps, float* state, size_t state_stride,
+                      size_t conv_off, const int32_t* seq_start, const int32_t* seq_slot, int sequences, int C,
+                      cudaStream_t stream);
+// The state-space mixer's preparation.  proj [rows, proj_stride] = z (H P) | x (H P) | B (G N) | C (G N) | dt (H); x, B, C
+// pass the convolution (with bias) and SiLU; prep [rows, 2 G N + H P + 2 H] = C | B | x | softplus(dt + dt_bias) |
+// exp(-exp(a_log) dt): what citlali_delta_rule in mode 2 reads with KH = G, D = N, V = P.  Keeps the last inputs.
+int citlali_ssm_prepare(const float* proj, int proj_stride, const float* taps_w, int taps, const float* conv_bias, float* state,
+                        size_t state_stride, size_t conv_off, const int32_t* row_slot, const int32_t* seq_start,
+                        const int32_t* seq_slot, int sequences, const float* a_log, const float* dt_bias, float* prep, int rows,
+                        int H, int P, int G, int N, cudaStream_t stream);
+// y = (o + skip[h] x) * silu(z), divided by the root mean square of its norm group (`groups` equal parts of a row, eps
+// inside the root), times weight.  x = prep[row, x_col ...], z = proj[row, 0 ...].
+int citlali_ssm_output(const float* o, const float* prep, int prep_stride, int x_col, const float* proj, int proj_stride,
+                       const float* skip, const float* weight, void* y, int y_dtype, int rows, int H, int P, int groups,
+                       float eps, cudaStream_t stream);
+// The gates of a linear recurrent unit.  u [rows, width] in `blocks` equal parts; per part b: r = sigmoid(Wa_b u_b + ba_b),
+// i = sigmoid(Wi_b u_b + bi_b), the matrices given transposed [blocks, in, out]; a = exp(-8 r softplus(lam)),
+// coef = sqrt(1 - a^2) i u.
+int citlali_lru_gates(const float* u, const float* wa_t, const float* ba, const float* wi_t, const float* bi, const float* lam,
+                      float* a_out, float* coef_out, int rows, int width, int blocks, cudaStream_t stream);
+// S <- a S + coef per channel over each sequence's rows, from and into state[slot][state_off ...]; out[row] = S *
+// gelu_tanh(side[row] + side_bias).
+int citlali_gated_scan(const float* a, const float* coef, const float* side, int side_stride, const float* side_bias,
+                       float* state, size_t state_stride, size_t state_off, const int32_t* seq_start, const int32_t* seq_slot,
+                       int sequences, void* out, int out_dtype, int width, cudaStream_t stream);
+
+// ---- attention over a window that keeps the first tokens ------------------------------------------------------------
+// proj [rows, proj_stride] float32 = q (nq d) | k (nkv d) | v (nkv vd).  Every channel passes a causal convolution (taps_w
+// [C, taps], no bias; kept inputs as in citlali_causal_conv; the caller stores them afterwards with citlali_conv_keep); q and
+// k heads then an RMS norm with q_gain / k_gain [d] (null: none) and the rotation of elements (2i, 2i+1), 2i < rot_dims, by
+// position * inv_freq[i].  q goes to q_out [rows, nq d]; with write_cache k and v go to the paged pools
+// [page, nkv, page_size, d] and [page, nkv, page_size, vd].
+int citlali_conv_heads_prepare(const float* proj, int proj_stride, const float* taps_w, int taps, float* state,
+                               size_t state_stride, size_t conv_off, const float* q_gain, const float* k_gain,
+                               const float* inv_freq, int rot_dims, const int32_t* row_slot, const int32_t* row_pos,
+                               const int32_t* page_table, int table_stride, void* k_pool, void* v_pool, int cache_dtype,
+                               int page_size, void* q_out, int q_dtype, int rows, int nq, int nkv, int d, int vd, float eps,
+                               int write_cache, cudaStream_t stream);
+// out [rows, nq vd]: softmax attention of every row over the keys j <= pos of its slot with pos - j < window or
+// j < keep_first (window 0: all keys).  max_keys bounds the keys a row sees (shared memory).
+int citlali_attention_window(const void* q, int q_dtype, const void* k_pool, const void* v_pool, int cache_dtype,
+                             const int32_t* page_table, int table_stride, const int32_t* row_slot, const int32_t* row_pos,
+                             void* out, int rows, int nq, int nkv, int d, int vd, int page_size, int window, int keep_first,
+                             int max_keys, float scale, cudaStream_t stream);
+
+// ---- routed experts ----------------------------------------------------------------------------------------------------
+// weights [rows, E] = softmax(logits) at the `top` best experts among those of the `keep` best of `groups` equal groups of
+// neighbours (a group's score is its largest score; groups <= 1: no groups), 0 elsewhere; chosen [rows, top] (may be
+// null) their indices, best first.
+int citlali_moe_route(const float* logits, float* weights, int32_t* chosen, int rows, int E, int groups, int keep, int top,
+                      cudaStream_t stream);
+// act[r, e, :] *= weights[r, e] over act [rows, E, ff].
+int citlali_moe_scale(void* act, int dtype, const float* weights, int rows, int E, int ff, cudaStream_t stream);
 
 // ---- attention through a shared latent -------------------------------------------------------------------------
 // proj [rows, proj_stride] float32 = query latent (RQ) | latent (R) | shared key part (P) | ...; cq [rows, RQ] receives

@@ -26,6 +26,19 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
+// A row's write strengths beta_h = sigmoid(row[beta_col + h]) and decays.  One decay a head: g_h = exp(-exp(a_log[h])
+// softplus(pre[h] + dt_bias[h])), pre = row[decay_col ...] or, if given, decay_row.  One a key channel (GD = D):
+// g_(h,i) = exp(-exp(a_log[h]) softplus(decay_row[h D + i] + dt_bias[h D + i])).  dst receives beta [H] | g [H GD].  All threads of the block take part.
+__device__ __forceinline__ void write_strength_and_decay(const float* __restrict__ row, int beta_col, int decay_col,
+                                                         const float* __restrict__ decay_row, const float* __restrict__ a_log,
+                                                         const float* __restrict__ dt_bias, float* __restrict__ dst, int H, int GD) {
+    for (int h = threadIdx.x; h < H; h += blockDim.x) dst[h] = sigmoidf_(row[beta_col + h]);
+    for (int i = threadIdx.x; i < H * GD; i += blockDim.x) {
+        const float pre = decay_row ? decay_row[i] : row[decay_col + i];
+        dst[H + i] = expf(-expf(a_log[i / GD]) * softplusf_(pre + dt_bias[i]));
+    }
+}
+
 // proj [rows, proj_stride] float32 holds, per row: q (KH*D) | k (KH*D) | v (H*V) | gate (H*V) | b (H) | a (H).
 // prep [rows, C + 2H] receives q^ | k^ | v | beta | g, C = 2 KH D + H V.
 // conv_state [slot] is [taps-1, C]: the inputs at the sequence's last taps-1 positions, oldest first.
@@ -33,21 +46,19 @@ __global__ void __launch_bounds__(256)
 delta_prepare_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ taps_w, int taps,
                      const float* __restrict__ state, size_t state_stride, size_t conv_off,
                      const int32_t* __restrict__ row_slot, const float* __restrict__ a_log,
-                     const float* __restrict__ dt_bias, float* __restrict__ prep, int H, int KH, int D, int V, float unit_eps) {
+                     const float* __restrict__ dt_bias, float* __restrict__ prep, int H, int KH, int D, int V, float unit_eps,
+                     int beta_col, int decay_col, const float* __restrict__ decay_in, int decay_stride, int channel_decay) {
     dependents_may_launch();
     wait_for_predecessor();
     // A warp: one row and one segment of its channels (a q head, a k head, or a head's values); eight segments a block.
     const int row = blockIdx.x, lane = threadIdx.x & 31;
     const int seg = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int C = 2 * KH * D + H * V;
-    float* dst = prep + (size_t)row * (C + 2 * H);
-    if (blockIdx.y == 0 && threadIdx.x < H) {                 // the head's write strength and decay
-        const float* rest = proj + (size_t)row * proj_stride + C + H * V;
-        for (int h = threadIdx.x; h < H; h += blockDim.x) {
-            dst[C + h] = sigmoidf_(rest[h]);
-            dst[C + H + h] = expf(-expf(a_log[h]) * softplusf_(rest[H + h] + dt_bias[h]));
-        }
-    }
+    const int GD = channel_decay ? D : 1;                          // decays a head: one, or one a key channel
+    float* dst = prep + (size_t)row * (C + H + H * GD);
+    if (blockIdx.y == 0) write_strength_and_decay(proj + (size_t)row * proj_stride, beta_col, decay_col,
+                                                  decay_in ? decay_in + (size_t)row * decay_stride : nullptr, a_log, dt_bias,
+                                                  dst + C, H, GD);
     if (seg >= 2 * KH + H) return;
     const bool unit = seg < 2 * KH;                           // q and k heads are made unit vectors
     const int c0 = unit ? seg * D : 2 * KH * D + (seg - 2 * KH) * V, n = unit ? D : V;
@@ -101,7 +112,8 @@ __global__ void __launch_bounds__(128)
 delta_prepare_block_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ taps_w, int taps,
                      const float* __restrict__ state, size_t state_stride, size_t conv_off,
                      const int32_t* __restrict__ row_slot, const float* __restrict__ a_log,
-                     const float* __restrict__ dt_bias, float* __restrict__ prep, int H, int KH, int D, int V, float unit_eps) {
+                     const float* __restrict__ dt_bias, float* __restrict__ prep, int H, int KH, int D, int V, float unit_eps,
+                     int beta_col, int decay_col, const float* __restrict__ decay_in, int decay_stride, int channel_decay) {
     extern __shared__ float act[];          // max(D, V) floats
     __shared__ float scratch[32];
     dependents_may_launch();
@@ -135,15 +147,12 @@ delta_prepare_block_kernel(const float* __restrict__ proj, int proj_stride, cons
         f = 1.0f / sqrtf(ss + unit_eps);
         if (seg < KH) f /= sqrtf((float)D);
     }
-    float* dst = prep + (size_t)row * (C + 2 * H);
+    const int GD = channel_decay ? D : 1;
+    float* dst = prep + (size_t)row * (C + H + H * GD);
     for (int i = threadIdx.x; i < n; i += blockDim.x) dst[c0 + i] = act[i] * f;      // a thread reads back what it wrote
-    if (seg == 0) {
-        const float* rest = proj + (size_t)row * proj_stride + C + H * V;
-        for (int h = threadIdx.x; h < H; h += blockDim.x) {
-            dst[C + h] = sigmoidf_(rest[h]);
-            dst[C + H + h] = expf(-expf(a_log[h]) * softplusf_(rest[H + h] + dt_bias[h]));
-        }
-    }
+    if (seg == 0) write_strength_and_decay(proj + (size_t)row * proj_stride, beta_col, decay_col,
+                                           decay_in ? decay_in + (size_t)row * decay_stride : nullptr, a_log, dt_bias,
+                                           dst + C, H, GD);
 }
 
 // After the step's rows were convolved: the sequence keeps its last taps-1 inputs.  One thread a channel.
@@ -170,13 +179,18 @@ __global__ void delta_conv_state_kernel(const float* __restrict__ proj, int proj
 // memory; eight lanes a column were measured slower: a token's fixed work then weighs more than its sums).  DP: the head size rounded up to a multiple of 32; rows of S beyond D stay zero.  The two dot products of a
 // token are summed over a lane's rows first and over the four lanes after, in one fixed order.  The inputs of the next
 // tokens (seven, or three for heads over 128) are on their way into a ring in shared memory (cp.async) while the current token is computed.
-template <int DP>
+// MODE 0: one decay a head.  MODE 1: a decay a key channel (row i of S is multiplied by g_i; the token's D decays follow
+// its query in the ring).  MODE 2: no correction term, u = beta v (a state-space recurrence S <- g S + beta k v^T,
+// o = S^T q, with the step size as beta).
+template <int DP, int MODE>
 __global__ void __launch_bounds__(128)
 delta_rule_kernel(const float* __restrict__ prep, int prep_stride, float* __restrict__ state, size_t state_stride,
                   const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot, int sequences,
                   int H, int KH, int D, int V, float* __restrict__ out, int pairs) {
-    constexpr int STAGES = DP <= 128 ? 8 : 4;    // tokens in flight from global memory: a warp is alone with their latency
-    constexpr int STRIDE = 2 * DP + 16;          // floats a token takes in the ring: k | q | v of 8 columns | beta | g
+    // tokens in flight from global memory (a warp is alone with their latency); fewer where a token takes more of the 48 KB
+    constexpr int STAGES = MODE == 1 ? (DP <= 96 ? 8 : (DP <= 192 ? 4 : 3)) : (DP <= 128 ? 8 : 4);
+    constexpr int VOFF = MODE == 1 ? 3 * DP : 2 * DP;   // where a token's scalars start in its place of the ring
+    constexpr int STRIDE = VOFF + 16;            // floats a token takes in the ring: k | q | (decays) | v of 8 columns | beta | g
     __shared__ __align__(16) float ring[4][STAGES][STRIDE];
     dependents_may_launch();
     wait_for_predecessor();
@@ -216,17 +230,18 @@ delta_rule_kernel(const float* __restrict__ prep, int prep_stride, float* __rest
                 if (i < D) {
                     cp_async4(dst + i, p + (KH + kv_head) * D + i);
                     cp_async4(dst + DP + i, p + kv_head * D + i);
+                    if (MODE == 1) cp_async4(dst + 2 * DP + i, p + C + H + head * D + i);
                 }
             }
-            if (lane < 8 && chunk * 8 + lane < V) cp_async4(dst + 2 * DP + lane, p + 2 * KH * D + head * V + chunk * 8 + lane);
-            if (lane == 8) cp_async4(dst + 2 * DP + 8, p + C + head);
-            if (lane == 9) cp_async4(dst + 2 * DP + 9, p + C + H + head);
+            if (lane < 8 && chunk * 8 + lane < V) cp_async4(dst + VOFF + lane, p + 2 * KH * D + head * V + chunk * 8 + lane);
+            if (lane == 8) cp_async4(dst + VOFF + 8, p + C + head);
+            if (MODE != 1 && lane == 9) cp_async4(dst + VOFF + 9, p + C + H + head);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     for (int s = 0; s < STAGES - 1; ++s) issue(r0 + s);
     int row = r0;
-    if (pairs) {
+    if (MODE == 0 && pairs) {
         // Two tokens at a time.  With S the state before both, every sum over the rows of S is taken against S itself,
         //   a1 = S^T k1, a2 = S^T k2, b1 = S^T q1, b2 = S^T q2   (four independent chains over the lane's rows),
         // and the rest are scalars of the head (k1.k2, q1.k1, q2.k1, q2.k2) and of the column:
@@ -309,18 +324,32 @@ delta_rule_kernel(const float* __restrict__ prep, int prep_stride, float* __rest
         const float* cur = ring[warp][(row - r0) % STAGES];
         const float* ks = cur;
         const float* qs = cur + DP;
-        const float v = cur[2 * DP + (lane >> 2)], beta = cur[2 * DP + 8], g = cur[2 * DP + 9];
-        float sk0 = 0.0f, sk1 = 0.0f, sk2 = 0.0f, sk3 = 0.0f;
+        const float v = cur[VOFF + (lane >> 2)], beta = cur[VOFF + 8];
+        const float g = MODE == 1 ? 1.0f : cur[VOFF + 9];
+        if (MODE == 1) {                         // every row of S decays by its own factor before it is read
+            const float* gs = cur + 2 * DP;
 #pragma unroll
-        for (int j = 0; j < GROUPS; ++j) {
-            const float4 k4 = *reinterpret_cast<const float4*>(ks + (4 * j + part) * 4);
-            sk0 = fmaf(S[j][0], k4.x, sk0); sk1 = fmaf(S[j][1], k4.y, sk1);
-            sk2 = fmaf(S[j][2], k4.z, sk2); sk3 = fmaf(S[j][3], k4.w, sk3);
+            for (int j = 0; j < GROUPS; ++j) {
+                const float4 g4 = *reinterpret_cast<const float4*>(gs + (4 * j + part) * 4);
+                S[j][0] *= g4.x; S[j][1] *= g4.y; S[j][2] *= g4.z; S[j][3] *= g4.w;
+            }
         }
-        float sk = (sk0 + sk1) + (sk2 + sk3);
-        sk += __shfl_xor_sync(0xffffffffu, sk, 1);
-        sk += __shfl_xor_sync(0xffffffffu, sk, 2);
-        const float u = beta * (v - g * sk);
+        float u;
+        if (MODE == 2) {
+            u = beta * v;
+        } else {
+            float sk0 = 0.0f, sk1 = 0.0f, sk2 = 0.0f, sk3 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < GROUPS; ++j) {
+                const float4 k4 = *reinterpret_cast<const float4*>(ks + (4 * j + part) * 4);
+                sk0 = fmaf(S[j][0], k4.x, sk0); sk1 = fmaf(S[j][1], k4.y, sk1);
+                sk2 = fmaf(S[j][2], k4.z, sk2); sk3 = fmaf(S[j][3], k4.w, sk3);
+            }
+            float sk = (sk0 + sk1) + (sk2 + sk3);
+            sk += __shfl_xor_sync(0xffffffffu, sk, 1);
+            sk += __shfl_xor_sync(0xffffffffu, sk, 2);
+            u = beta * (v - g * sk);
+        }
         float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
         for (int j = 0; j < GROUPS; ++j) {
@@ -348,11 +377,12 @@ delta_rule_kernel(const float* __restrict__ prep, int prep_stride, float* __rest
     }
 }
 
-// y[row, h, :] = o[row, h, :] / sqrt(mean(o^2) + eps) * weight * silu(gate[row, h, :]).  One warp a head.
+// y[row, h, :] = o[row, h, :] / sqrt(mean(o^2) + eps) * weight * act(gate[row, h, :]), act = SiLU (gate_act 0) or the
+// sigmoid (1).  One warp a head.
 template <typename TO>
 __global__ void __launch_bounds__(256)
 delta_output_kernel(const float* __restrict__ o, const float* __restrict__ gate, int gate_stride,
-                    const float* __restrict__ weight, TO* __restrict__ y, int H, int V, float eps) {
+                    const float* __restrict__ weight, TO* __restrict__ y, int H, int V, float eps, int gate_act) {
     dependents_may_launch();
     wait_for_predecessor();
     const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -364,7 +394,7 @@ delta_output_kernel(const float* __restrict__ o, const float* __restrict__ gate,
         const float inv = 1.0f / sqrtf(ss / (float)V + eps);
         const float* gt = gate + (size_t)row * gate_stride + h * V;
         for (int i = lane; i < V; i += 32)
-            stf(y, ((size_t)row * H + h) * V + i, src[i] * inv * weight[i] * siluf_(gt[i]));
+            stf(y, ((size_t)row * H + h) * V + i, src[i] * inv * weight[i] * (gate_act == 1 ? sigmoidf_(gt[i]) : siluf_(gt[i])));
     }
 }
 
@@ -376,10 +406,11 @@ extern "C" int citlali_delta_prepare(const float* proj, int proj_stride, const f
                                      size_t state_stride, size_t conv_off, const int32_t* row_slot,
                                      const int32_t* seq_start, const int32_t* seq_slot, int sequences,
                                      const float* a_log, const float* dt_bias, float* prep, int rows, int H, int KH,
-                                     int D, int V, float unit_eps, int block_a_segment, cudaStream_t stream) {
+                                     int D, int V, float unit_eps, int block_a_segment, int beta_col, int decay_col,
+                                     const float* decay_in, int decay_stride, int channel_decay, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (H <= 0 || KH <= 0 || H % KH != 0 || D <= 0 || V <= 0 || taps < 1) {
-        set_last_error("delta_prepare: %d heads over %d key heads of %d, values of %d, %d taps", H, KH, D, V, taps);
+    if (H <= 0 || KH <= 0 || H % KH != 0 || D <= 0 || V <= 0 || taps < 1 || (channel_decay && !decay_in)) {
+        set_last_error("delta_prepare: %d heads over %d key heads of %d, values of %d, %d taps (a decay per channel comes in a buffer of its own)", H, KH, D, V, taps);
         return kBadShape;
     }
     const int C = 2 * KH * D + H * V;
@@ -396,11 +427,13 @@ extern "C" int citlali_delta_prepare(const float* proj, int proj_stride, const f
         }
         dim3 prepare_grid(rows, segments);
         launch_kernel(delta_prepare_block_kernel, prepare_grid, 128, smem, stream, proj, proj_stride, taps_w, taps,
-                      (const float*)state, state_stride, conv_off, row_slot, a_log, dt_bias, prep, H, KH, D, V, unit_eps);
+                      (const float*)state, state_stride, conv_off, row_slot, a_log, dt_bias, prep, H, KH, D, V, unit_eps,
+                      beta_col, decay_col, decay_in, decay_stride, channel_decay);
     } else {
         dim3 prepare_grid(rows, (segments + 7) / 8);
         launch_kernel(delta_prepare_kernel, prepare_grid, 256, 0, stream, proj, proj_stride, taps_w, taps, (const float*)state,
-                      state_stride, conv_off, row_slot, a_log, dt_bias, prep, H, KH, D, V, unit_eps);
+                      state_stride, conv_off, row_slot, a_log, dt_bias, prep, H, KH, D, V, unit_eps, beta_col, decay_col,
+                      decay_in, decay_stride, channel_decay);
     }
     int code = CITLALI_LAUNCH_CHECK();
     if (code != 0 || taps == 1) return code;
@@ -410,18 +443,14 @@ extern "C" int citlali_delta_prepare(const float* proj, int proj_stride, const f
     return CITLALI_LAUNCH_CHECK();
 }
 
-extern "C" int citlali_delta_rule(const float* prep, int prep_stride, float* state, size_t state_stride,
-                                  const int32_t* seq_start, const int32_t* seq_slot, int sequences, int H, int KH, int D,
-                                  int V, float* out, int pairs, cudaStream_t stream) {
-    if (sequences <= 0) return 0;
-    if (D > 256) {
-        set_last_error("delta_rule: a head size of %d exceeds 256", D);
-        return kTooLarge;
-    }
+template <int MODE>
+static int launch_delta_rule(const float* prep, int prep_stride, float* state, size_t state_stride, const int32_t* seq_start,
+                             const int32_t* seq_slot, int sequences, int H, int KH, int D, int V, float* out, int pairs,
+                             cudaStream_t stream) {
     const long units = (long)sequences * H * ((V + 7) / 8);
     const int blocks = (int)((units + 3) / 4);
 #define CITLALI_DELTA(DP)                                                                                         \
-    launch_kernel(delta_rule_kernel<DP>, blocks, 128, 0, stream, prep, prep_stride, state, state_stride, seq_start, \
+    launch_kernel(delta_rule_kernel<DP, MODE>, blocks, 128, 0, stream, prep, prep_stride, state, state_stride, seq_start, \
                   seq_slot, sequences, H, KH, D, V, out, pairs)
     switch ((D + 31) / 32) {
         case 1: CITLALI_DELTA(32); break;
@@ -437,12 +466,29 @@ extern "C" int citlali_delta_rule(const float* prep, int prep_stride, float* sta
     return CITLALI_LAUNCH_CHECK();
 }
 
+extern "C" int citlali_delta_rule(const float* prep, int prep_stride, float* state, size_t state_stride,
+                                  const int32_t* seq_start, const int32_t* seq_slot, int sequences, int H, int KH, int D,
+                                  int V, float* out, int pairs, int mode, cudaStream_t stream) {
+    if (sequences <= 0) return 0;
+    if (D > 256) {
+        set_last_error("delta_rule: a head size of %d exceeds 256", D);
+        return kTooLarge;
+    }
+    if (mode < 0 || mode > 2 || H <= 0 || KH <= 0 || H % KH != 0) {
+        set_last_error("delta_rule: form %d, %d heads over %d key heads", mode, H, KH);
+        return kBadShape;
+    }
+    if (mode == 1) return launch_delta_rule<1>(prep, prep_stride, state, state_stride, seq_start, seq_slot, sequences, H, KH, D, V, out, 0, stream);
+    if (mode == 2) return launch_delta_rule<2>(prep, prep_stride, state, state_stride, seq_start, seq_slot, sequences, H, KH, D, V, out, 0, stream);
+    return launch_delta_rule<0>(prep, prep_stride, state, state_stride, seq_start, seq_slot, sequences, H, KH, D, V, out, pairs, stream);
+}
+
 extern "C" int citlali_delta_output(const float* o, const float* gate, int gate_stride, const float* weight, void* y,
-                                    int y_dtype, int rows, int H, int V, float eps, cudaStream_t stream) {
+                                    int y_dtype, int rows, int H, int V, float eps, int gate_act, cudaStream_t stream) {
     if (rows <= 0) return 0;
     return CITLALI_DISPATCH_FLOAT(y_dtype, TO, [&] {
         dim3 grid(rows, (H + 7) / 8 < 64 ? (H + 7) / 8 : 64);             // a warp a head, eight heads a block
-        launch_kernel(delta_output_kernel<TO>, grid, 256, 0, stream, o, gate, gate_stride, weight, (TO*)y, H, V, eps);
+        launch_kernel(delta_output_kernel<TO>, grid, 256, 0, stream, o, gate, gate_stride, weight, (TO*)y, H, V, eps, gate_act);
         return CITLALI_LAUNCH_CHECK();
     });
 }

@@ -1,0 +1,224 @@
+// Attention over a sliding window that also keeps a sequence's first tokens, for heads whose keys and values may differ
+// in size, with a short causal convolution in front of q, k and v.
+//
+//   conv_heads_prepare   one warp a (row, head): the convolution over time of the head's channels (earlier tokens from the
+//                        step's rows or from the sequence's kept inputs), for q and k heads an RMS norm with a weight
+//                        shared by the heads and the rotation of the first rot_dims elements in neighbouring pairs
+//                        (2i, 2i+1) by position * inv_freq[i]; q goes to a buffer, k and v to the row's place in the
+//                        paged cache.  All float32 until the one rounding at the store.
+//   attention_window     one block a (row, query head): keys j <= pos with pos - j < window or j < keep_first (window 0:
+//                        every key); scores, softmax and the weighted sum in float32 in one fixed order, so a row's result
+//                        does not depend on the step it came in.
+#include "api.h"
+#include "common.cuh"
+
+namespace citlali {
+
+constexpr int kHeadWarps = 8;
+constexpr int kMaxPerLane = 8;         // head sizes up to 256
+
+template <typename T, typename TQ>
+__global__ void __launch_bounds__(kHeadWarps * 32)
+conv_heads_prepare_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ taps_w, int taps,
+                          const float* __restrict__ state, size_t state_stride, size_t conv_off,
+                          const float* __restrict__ q_gain, const float* __restrict__ k_gain, const float* __restrict__ inv_freq,
+                          int rot_dims, const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
+                          const int32_t* __restrict__ page_table, int table_stride, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                          int page_size, TQ* __restrict__ q_out, int nq, int nkv, int d, int vd, float eps, int write_cache) {
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.x, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * kHeadWarps + (threadIdx.x >> 5);
+    if (head >= nq + 2 * nkv) return;
+    const bool is_q = head < nq, is_v = head >= nq + nkv;
+    if (!is_q && !write_cache) return;
+    const int C = (nq + nkv) * d + nkv * vd;
+    const int n = is_v ? vd : d;
+    const int c0 = is_v ? (nq + nkv) * d + (head - nq - nkv) * vd : head * d;
+    const int slot = row_slot[row], pos = row_pos[row];
+    int in_step = 0;
+    while (in_step < taps - 1 && row - in_step - 1 >= 0 && row_slot[row - in_step - 1] == slot) ++in_step;
+    const float* kept = state ? state + (size_t)slot * state_stride + conv_off : nullptr;
+    float x[kMaxPerLane];
+    float ss = 0.0f;
+    // a lane holds the neighbouring elements 2 lane, 2 lane + 1 (+ 64 j): a rotation pair stays in one lane
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+        const int i = (j >> 1) * 64 + 2 * lane + (j & 1);
+        float acc = 0.0f;
+        if (i < n) {
+            const int c = c0 + i;
+            for (int back = taps - 1; back >= 0; --back) {
+                float u;
+                if (back <= in_step) u = proj[(size_t)(row - back) * proj_stride + c];
+                else u = kept[(size_t)(taps - 1 - back + in_step) * C + c];
+                acc = fmaf(taps_w[(size_t)c * taps + (taps - 1 - back)], u, acc);
+            }
+        }
+        x[j] = acc;
+        ss = fmaf(acc, acc, ss);
+    }
+    size_t cache_at = 0;
+    if (!is_q) {
+        const int page = page_table[(size_t)slot * table_stride + pos / page_size];
+        const int kvh = is_v ? head - nq - nkv : head - nq;
+        cache_at = (((size_t)page * nkv + kvh) * page_size + pos % page_size) * (size_t)n;
+    }
+    if (is_v) {
+#pragma unroll
+        for (int j = 0; j < kMaxPerLane; ++j) {
+            const int i = (j >> 1) * 64 + 2 * lane + (j & 1);
+            if (i < n) stf(v_pool, cache_at + i, x[j]);
+        }
+        return;
+    }
+    const float* gain = is_q ? q_gain : k_gain;
+    if (gain) {
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+        for (int j = 0; j < kMaxPerLane; ++j) {
+            const int i = (j >> 1) * 64 + 2 * lane + (j & 1);
+            if (i < n) x[j] = x[j] * inv * gain[i];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; j += 2) {
+        const int i = (j >> 1) * 64 + 2 * lane;
+        if (i < rot_dims) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i >> 1], &sn, &cs);
+            const float a = x[j], b = x[j + 1];
+            x[j] = a * cs - b * sn;
+            x[j + 1] = b * cs + a * sn;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+        const int i = (j >> 1) * 64 + 2 * lane + (j & 1);
+        if (i < n) {
+            if (is_q) stf(q_out, (size_t)row * nq * d + (size_t)head * d + i, x[j]);
+            else stf(k_pool, cache_at + i, x[j]);
+        }
+    }
+}
+
+template <typename T, typename TQ>
+__global__ void __launch_bounds__(128)
+attention_window_kernel(const TQ* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
+                        const int32_t* __restrict__ page_table, int table_stride, const int32_t* __restrict__ row_slot,
+                        const int32_t* __restrict__ row_pos, TQ* __restrict__ out, int nq, int nkv, int d, int vd,
+                        int page_size, int window, int keep_first, float scale) {
+    extern __shared__ float smem[];
+    __shared__ float scratch[32];
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.x, head = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = head / (nq / nkv);
+    const int pos = row_pos[row];
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first = min(keep_first, lo);                 // kept keys 0..first-1, then the window lo..pos
+    const int n = first + pos - lo + 1;
+    float* qs = smem;          // d
+    float* sc = smem + d;      // n
+    const int32_t* pages = page_table + (size_t)row_slot[row] * table_stride;
+    const TQ* qrow = q + (size_t)row * nq * d + (size_t)head * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) qs[i] = ldf(qrow, i);
+    __syncthreads();
+    for (int t = warp; t < n; t += 4) {
+        const int key = t < first ? t : lo + (t - first);
+        const T* krow = k_pool + (((size_t)pages[key / page_size] * nkv + g) * page_size + key % page_size) * d;
+        float s = 0.0f;
+        for (int i = lane; i < d; i += 32) s = fmaf(qs[i], ldf(krow, i), s);
+        s = warp_sum(s);
+        if (lane == 0) sc[t] = s * scale;
+    }
+    __syncthreads();
+    float m = -INFINITY;
+    for (int t = threadIdx.x; t < n; t += blockDim.x) m = fmaxf(m, sc[t]);
+    m = block_max(m, scratch);
+    float z = 0.0f;
+    for (int t = threadIdx.x; t < n; t += blockDim.x) {
+        const float e = expf(sc[t] - m);
+        sc[t] = e;
+        z += e;
+    }
+    z = block_sum(z, scratch);
+    const float inv_z = 1.0f / z;
+    __syncthreads();
+    for (int i = threadIdx.x; i < vd; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int t = 0; t < n; ++t) {
+            const int key = t < first ? t : lo + (t - first);
+            const T* vrow = v_pool + (((size_t)pages[key / page_size] * nkv + g) * page_size + key % page_size) * vd;
+            acc = fmaf(sc[t], ldf(vrow, i), acc);
+        }
+        stf(out, (size_t)row * nq * vd + (size_t)head * vd + i, acc * inv_z);
+    }
+}
+
+}  // namespace citlali
+
+using namespace citlali;
+
+extern "C" int citlali_conv_heads_prepare(const float* proj, int proj_stride, const float* taps_w, int taps, float* state,
+                                          size_t state_stride, size_t conv_off, const float* q_gain, const float* k_gain,
+                                          const float* inv_freq, int rot_dims, const int32_t* row_slot, const int32_t* row_pos,
+                                          const int32_t* page_table, int table_stride, void* k_pool, void* v_pool,
+                                          int cache_dtype, int page_size, void* q_out, int q_dtype, int rows, int nq, int nkv,
+                                          int d, int vd, float eps, int write_cache, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (nq <= 0 || nkv <= 0 || d <= 0 || vd <= 0 || d > 32 * kMaxPerLane || vd > 32 * kMaxPerLane || taps < 1 || page_size <= 0) {
+        set_last_error("conv_heads_prepare: %d and %d heads of %d (values %d, at most %d), %d taps", nq, nkv, d, vd,
+                       32 * kMaxPerLane, taps);
+        return kBadShape;
+    }
+    if (rot_dims < 0 || rot_dims % 2 != 0 || rot_dims > d || (taps > 1 && state == nullptr)) {
+        set_last_error("conv_heads_prepare: %d rotated elements must be even and at most the head size %d; taps need a state",
+                       rot_dims, d);
+        return kBadShape;
+    }
+    const int heads = nq + 2 * nkv;
+    dim3 grid(rows, (heads + kHeadWarps - 1) / kHeadWarps);
+    return CITLALI_DISPATCH_FLOAT(cache_dtype, T, [&] {
+        return CITLALI_DISPATCH_FLOAT(q_dtype, TQ, [&] {
+            launch_kernel(conv_heads_prepare_kernel<T, TQ>, grid, kHeadWarps * 32, 0, stream, proj, proj_stride, taps_w, taps,
+                          (const float*)state, state_stride, conv_off, q_gain, k_gain, inv_freq, rot_dims, row_slot, row_pos,
+                          page_table, table_stride, (T*)k_pool, (T*)v_pool, page_size, (TQ*)q_out, nq, nkv, d, vd, eps,
+                          write_cache);
+            return CITLALI_LAUNCH_CHECK();
+        });
+    });
+}
+
+extern "C" int citlali_attention_window(const void* q, int q_dtype, const void* k_pool, const void* v_pool, int cache_dtype,
+                                        const int32_t* page_table, int table_stride, const int32_t* row_slot,
+                                        const int32_t* row_pos, void* out, int rows, int nq, int nkv, int d, int vd,
+                                        int page_size, int window, int keep_first, int max_keys, float scale,
+                                        cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || vd <= 0 || nq > 65535 || window < 0 || keep_first < 0) {
+        set_last_error("attention_window: %d query heads over %d key/value heads of %d (values %d), window %d, %d kept", nq, nkv,
+                       d, vd, window, keep_first);
+        return kBadShape;
+    }
+    const size_t smem = (size_t)(d + max_keys) * sizeof(float);
+    if (smem > 200 * 1024) {
+        set_last_error("attention_window: %d keys for one row need %zu bytes of shared memory, more than 204800", max_keys, smem);
+        return kTooLarge;
+    }
+    return CITLALI_DISPATCH_FLOAT(cache_dtype, T, [&] {
+        return CITLALI_DISPATCH_FLOAT(q_dtype, TQ, [&] {
+            auto kernel = attention_window_kernel<T, TQ>;
+            if (smem > 48 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e != cudaSuccess) return (int)e;
+            }
+            dim3 grid(rows, nq);
+            launch_kernel(kernel, grid, 128, smem, stream, (const TQ*)q, (const T*)k_pool, (const T*)v_pool, page_table,
+                          table_stride, row_slot, row_pos, (TQ*)out, nq, nkv, d, vd, page_size, window, keep_first, scale);
+            return CITLALI_LAUNCH_CHECK();
+        });
+    });
+}

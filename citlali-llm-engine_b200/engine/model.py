@@ -119,17 +119,20 @@ class DecoderModel:
             x = torch.empty((streams, batch.rows, spec.hidden_size), dtype=torch.float32, device=ctx.device)
             ops.embed_rows_streams(self.embedding, batch.tokens, x, ctx.error_flag, emb_scale)
         batch.norm_carry = None
+        batch.rows_carry = None
         batch.stream_write = None
         for i, step in enumerate(spec.schedule):
             source = i if step.cache_of is None else step.cache_of
             view = cache.view(source) if cache.has_view(source) else None
             # what the layer before left for this layer's first norm, if it left anything (parts/block.py)
             batch.norm_carry_in, batch.norm_carry = batch.norm_carry, None
+            batch.rows_carry_in, batch.rows_carry = batch.rows_carry, None
             if batch.stream_write is not None and not getattr(self.layers[step.layer], "takes_stream_write", False):
                 ops.hyper_write(x, *batch.stream_write)      # the block ahead left a write-back that this one would not do
                 batch.stream_write = None
             self.layers[step.layer].forward(x, batch, view, write_cache=step.cache_of is None)
         batch.norm_carry_in = batch.norm_carry = None
+        batch.rows_carry_in = batch.rows_carry = None
         if batch.stream_write is not None:              # the last layer's last write-back into the streams
             ops.hyper_write(x, *batch.stream_write)
             batch.stream_write = None

@@ -507,43 +507,238 @@ def relu_squared(x: torch.Tensor, y: torch.Tensor):
 # ---- the gated delta rule ------------------------------------------------------------------------
 
 def delta_prepare(proj, taps_w, state, conv_off, row_slot, seq_start, seq_slot, sequences, a_log, dt_bias, prep,
-                  H, KH, D, V, unit_eps, block_a_segment=False):
-    """See ``citlali_delta_prepare`` (csrc/api.h).  ``state`` [slots, n] float32; two launches unless taps == 1."""
+                  H, KH, D, V, unit_eps, block_a_segment=False, beta_col=None, decay_col=None, decay_in=None,
+                  channel_decay=False):
+    """See ``citlali_delta_prepare`` (csrc/api.h).  ``state`` [slots, n] float32; two launches unless taps == 1.
+    ``beta_col`` / ``decay_col``: the columns of b and a in a row of ``proj`` (default: behind q, k, v and a gate of H V
+    columns).  ``decay_in``: the decays' inputs in a tensor of their own (a view whose rows may be further apart than its
+    width).  ``channel_decay``: a decay per head and key channel, ``prep`` is then [rows, C + H + H D]."""
     _need_cuda(proj, taps_w, state, row_slot, seq_start, seq_slot, a_log, dt_bias, prep)
     rows = proj.shape[0]
     C = 2 * KH * D + H * V
     taps = taps_w.shape[1]
+    GD = D if channel_decay else 1
+    beta_col = C + H * V if beta_col is None else int(beta_col)
+    decay_col = beta_col + H if decay_col is None else int(decay_col)
     require(proj.dtype == torch.float32 and prep.dtype == torch.float32 and state.dtype == torch.float32
             and taps_w.dtype == torch.float32 and a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32,
             "delta_prepare: float32 tensors only")
-    require(proj.shape[1] >= C + H * V + 2 * H and prep.shape == (rows, C + 2 * H) and taps_w.shape[0] == C
+    require(proj.shape[1] >= beta_col + H and (decay_in is not None or proj.shape[1] >= decay_col + H)
+            and prep.shape == (rows, C + H + H * GD) and taps_w.shape[0] == C and dt_bias.numel() == H * GD
             and state.dim() == 2 and state.shape[1] >= conv_off + (taps - 1) * C, "delta_prepare: shapes do not fit")
+    require(not channel_decay or decay_in is not None, "delta_prepare: a decay per channel needs decay_in")
+    decay_stride = 0
+    if decay_in is not None:
+        require(decay_in.is_cuda and decay_in.dtype == torch.float32 and decay_in.shape == (rows, H * GD)
+                and decay_in.stride(1) == 1, "delta_prepare: the decays' inputs do not fit")
+        decay_stride = decay_in.stride(0)
     _check(lib().citlali_delta_prepare(_ptr(proj), _i(proj.shape[1]), _ptr(taps_w), _i(taps), _ptr(state),
                                        _sz(state.shape[1]), _sz(conv_off), _ptr(row_slot), _ptr(seq_start), _ptr(seq_slot),
                                        _i(sequences), _ptr(a_log), _ptr(dt_bias), _ptr(prep), _i(rows), _i(H), _i(KH),
-                                       _i(D), _i(V), _f(unit_eps), _i(1 if block_a_segment else 0), _stream()),
+                                       _i(D), _i(V), _f(unit_eps), _i(1 if block_a_segment else 0), _i(beta_col),
+                                       _i(decay_col), _ptr(decay_in), _i(decay_stride), _i(1 if channel_decay else 0),
+                                       _stream()),
            "delta_prepare" if taps == 1 else "delta_prepare_kept")
 
 
 _KERNELS_PER_CALL["delta_prepare_kept"] = 2
 
+DELTA_HEAD_DECAY, DELTA_CHANNEL_DECAY, DELTA_NO_CORRECTION = 0, 1, 2
 
-def delta_rule(prep, state, seq_start, seq_slot, sequences, H, KH, D, V, out, pairs=False):
+
+def delta_rule(prep, state, seq_start, seq_slot, sequences, H, KH, D, V, out, pairs=False, mode=DELTA_HEAD_DECAY):
+    """``mode``: one decay a head; a decay a key channel; or no correction term (u = beta v: a state-space recurrence)."""
     _need_cuda(prep, state, seq_start, seq_slot, out)
     require(prep.dtype == torch.float32 and state.dtype == torch.float32 and out.dtype == torch.float32
             and out.shape == (prep.shape[0], H * V) and state.shape[1] >= H * D * V, "delta_rule: shapes or dtypes do not fit")
+    require(prep.shape[1] == 2 * KH * D + H * V + H + H * (D if mode == DELTA_CHANNEL_DECAY else 1),
+            "delta_rule: the prepared rows' width does not fit the form")
     _check(lib().citlali_delta_rule(_ptr(prep), _i(prep.shape[1]), _ptr(state), _sz(state.shape[1]), _ptr(seq_start),
                                     _ptr(seq_slot), _i(sequences), _i(H), _i(KH), _i(D), _i(V), _ptr(out),
-                                    _i(1 if pairs else 0), _stream()), "delta_rule")
+                                    _i(1 if pairs else 0), _i(mode), _stream()), "delta_rule")
 
 
-def delta_output(o, gate, gate_stride, weight, y, H, V, eps):
-    """``gate``: a view into the projection's rows that starts at the gate's first column."""
+def delta_output(o, gate, gate_stride, weight, y, H, V, eps, gate_act="silu"):
+    """``gate``: a view into rows that starts at the gate's first column; ``gate_act``: "silu" or "sigmoid"."""
     _need_cuda(o, weight, y)
     require(gate.is_cuda and o.dtype == torch.float32 and gate.dtype == torch.float32 and weight.dtype == torch.float32
-            and weight.numel() == V and y.shape == o.shape, "delta_output: shapes or dtypes do not fit")
+            and weight.numel() == V and y.shape == o.shape and gate_act in ("silu", "sigmoid"),
+            "delta_output: shapes or dtypes do not fit")
     _check(lib().citlali_delta_output(_ptr(o), _ptr(gate), _i(gate_stride), _ptr(weight), _ptr(y), _i(_dtype_code(y)),
-                                      _i(o.shape[0]), _i(H), _i(V), _f(eps), _stream()), "delta_output")
+                                      _i(o.shape[0]), _i(H), _i(V), _f(eps), _i(1 if gate_act == "sigmoid" else 0), _stream()),
+           "delta_output")
+
+
+# ---- a norm on a sub-layer's output ---------------------------------------------------------------------
+
+def layer_norm_add(y, gain, eps, x, emit=None):
+    """``x += layer_norm(y) * gain`` (float32); ``emit`` receives the updated rows in its own dtype."""
+    _need_cuda(y, gain, x, emit)
+    rows, hidden = x.shape
+    require(y.dtype == torch.float32 and x.dtype == torch.float32 and y.shape == x.shape and gain.numel() == hidden
+            and (emit is None or emit.shape == x.shape), "layer_norm_add: shapes or dtypes do not fit")
+    _check(lib().citlali_layer_norm_add(_ptr(y), _ptr(gain), _i(_dtype_code(gain)), _ptr(x), _ptr(emit),
+                                        _i(_dtype_code(emit) if emit is not None else _F32), _i(rows), _i(hidden), _f(eps),
+                                        _stream()), "layer_norm_add")
+
+
+def layer_norm_rows(x, gain, eps, out, row_index=None):
+    _need_cuda(x, gain, out, row_index)
+    rows, hidden = out.shape
+    require(x.dtype == torch.float32 and x.shape[1] == hidden and gain.numel() == hidden
+            and (row_index is not None or x.shape[0] == rows)
+            and (row_index is None or (row_index.dtype == torch.int32 and row_index.numel() == rows)),
+            "layer_norm_rows: shapes or dtypes do not fit")
+    _check(lib().citlali_layer_norm_rows(_ptr(x), _ptr(gain), _i(_dtype_code(gain)), _ptr(row_index), _ptr(out),
+                                         _i(_dtype_code(out)), _i(rows), _i(hidden), _f(eps), _stream()), "layer_norm_rows")
+
+
+def cast_rows(x, out):
+    _need_cuda(x, out)
+    require(x.dtype == torch.float32 and x.shape == out.shape, "cast_rows: a float32 tensor and one of its shape")
+    _check(lib().citlali_cast_rows(_ptr(x), _ptr(out), _i(_dtype_code(out)), _sz(x.numel()), _stream()), "cast_rows")
+
+
+def scaled_sum(a, left, b, right, out):
+    """``out = a * left + b * right`` (float32; ``out`` may be one of them)."""
+    _need_cuda(left, right, out)
+    require(left.dtype == torch.float32 and right.dtype == torch.float32 and out.dtype == torch.float32
+            and left.shape == right.shape == out.shape, "scaled_sum: three float32 tensors of one shape")
+    _check(lib().citlali_scaled_sum(_f(a), _ptr(left), _f(b), _ptr(right), _ptr(out), _sz(out.numel()), _stream()), "scaled_sum")
+
+
+# ---- mixers with a state per sequence -----------------------------------------------------------------------
+
+def causal_conv(x, in_stride, taps_w, state, conv_off, batch, out, in_bias=None, bias=None, act=None, keep=True):
+    """A causal convolution over time of the first C columns of ``x`` (a view whose rows are ``in_stride`` floats apart),
+    C = ``taps_w.shape[0]``; see ``citlali_causal_conv``.  ``act``: None or "silu"."""
+    _need_cuda(taps_w, state, out, in_bias, bias)
+    C, taps = taps_w.shape
+    rows = out.shape[0]
+    require(x.is_cuda and x.dtype == torch.float32 and out.dtype == torch.float32 and taps_w.dtype == torch.float32
+            and out.shape[1] >= C and state.dtype == torch.float32 and state.shape[1] >= conv_off + (taps - 1) * C
+            and act in (None, "silu"), "causal_conv: shapes or dtypes do not fit")
+    _check(lib().citlali_causal_conv(_ptr(x), _i(in_stride), _ptr(in_bias), _ptr(taps_w), _i(taps), _ptr(bias),
+                                     _i(1 if act == "silu" else 0), _ptr(state), _sz(state.shape[1]), _sz(conv_off),
+                                     _ptr(batch.row_slot), _ptr(batch.seq_start), _ptr(batch.seq_slot), _i(batch.sequences),
+                                     _ptr(out), _i(out.shape[1]), _i(rows), _i(C), _i(1 if keep else 0), _stream()),
+           "causal_conv_kept" if (keep and taps > 1) else "causal_conv")
+
+
+_KERNELS_PER_CALL["causal_conv_kept"] = 2
+_KERNELS_PER_CALL["ssm_prepare_kept"] = 2
+
+
+def conv_keep(x, in_stride, taps, C, state, conv_off, batch, in_bias=None):
+    _need_cuda(state, in_bias)
+    if taps <= 1:
+        return
+    require(x.is_cuda and x.dtype == torch.float32 and state.shape[1] >= conv_off + (taps - 1) * C, "conv_keep: shapes do not fit")
+    _check(lib().citlali_conv_keep(_ptr(x), _i(in_stride), _ptr(in_bias), _i(taps), _ptr(state), _sz(state.shape[1]),
+                                   _sz(conv_off), _ptr(batch.seq_start), _ptr(batch.seq_slot), _i(batch.sequences), _i(C),
+                                   _stream()), "conv_keep")
+
+
+def ssm_prepare(proj, taps_w, conv_bias, state, conv_off, batch, a_log, dt_bias, prep, H, P, G, N):
+    _need_cuda(proj, taps_w, conv_bias, state, a_log, dt_bias, prep)
+    rows = proj.shape[0]
+    Cc = H * P + 2 * G * N
+    taps = taps_w.shape[1]
+    require(proj.dtype == torch.float32 and prep.dtype == torch.float32 and proj.shape[1] == H * P + Cc + H
+            and prep.shape == (rows, Cc + 2 * H) and taps_w.shape[0] == Cc and taps_w.dtype == torch.float32
+            and (conv_bias is None or conv_bias.numel() == Cc) and a_log.numel() == H and dt_bias.numel() == H
+            and state.shape[1] >= conv_off + (taps - 1) * Cc, "ssm_prepare: shapes or dtypes do not fit")
+    _check(lib().citlali_ssm_prepare(_ptr(proj), _i(proj.shape[1]), _ptr(taps_w), _i(taps), _ptr(conv_bias), _ptr(state),
+                                     _sz(state.shape[1]), _sz(conv_off), _ptr(batch.row_slot), _ptr(batch.seq_start),
+                                     _ptr(batch.seq_slot), _i(batch.sequences), _ptr(a_log), _ptr(dt_bias), _ptr(prep),
+                                     _i(rows), _i(H), _i(P), _i(G), _i(N), _stream()),
+           "ssm_prepare" if taps == 1 else "ssm_prepare_kept")
+
+
+def ssm_output(o, prep, x_col, proj, skip, weight, y, H, P, groups, eps):
+    _need_cuda(o, prep, proj, skip, weight, y)
+    require(o.dtype == torch.float32 and o.shape == (prep.shape[0], H * P) and y.shape == o.shape and skip.numel() == H
+            and weight.numel() == H * P and skip.dtype == torch.float32 and weight.dtype == torch.float32,
+            "ssm_output: shapes or dtypes do not fit")
+    _check(lib().citlali_ssm_output(_ptr(o), _ptr(prep), _i(prep.shape[1]), _i(x_col), _ptr(proj), _i(proj.shape[1]),
+                                    _ptr(skip), _ptr(weight), _ptr(y), _i(_dtype_code(y)), _i(o.shape[0]), _i(H), _i(P),
+                                    _i(groups), _f(eps), _stream()), "ssm_output")
+
+
+def lru_gates(u, wa_t, ba, wi_t, bi, lam, a_out, coef_out, blocks):
+    _need_cuda(u, wa_t, ba, wi_t, bi, lam, a_out, coef_out)
+    rows, width = u.shape
+    bw = width // max(blocks, 1)
+    require(all(t.dtype == torch.float32 for t in (u, wa_t, ba, wi_t, bi, lam, a_out, coef_out))
+            and wa_t.shape == (blocks, bw, bw) and wi_t.shape == (blocks, bw, bw) and ba.numel() == width
+            and bi.numel() == width and lam.numel() == width and a_out.shape == u.shape and coef_out.shape == u.shape,
+            "lru_gates: shapes or dtypes do not fit")
+    _check(lib().citlali_lru_gates(_ptr(u), _ptr(wa_t), _ptr(ba), _ptr(wi_t), _ptr(bi), _ptr(lam), _ptr(a_out),
+                                   _ptr(coef_out), _i(rows), _i(width), _i(blocks), _stream()), "lru_gates")
+
+
+def gated_scan(a, coef, side, side_stride, side_bias, state, state_off, batch, out):
+    _need_cuda(a, coef, side_bias, state, out)
+    rows, width = a.shape
+    require(a.dtype == torch.float32 and coef.shape == a.shape and side.is_cuda and side.dtype == torch.float32
+            and out.shape == a.shape and state.shape[1] >= state_off + width, "gated_scan: shapes or dtypes do not fit")
+    _check(lib().citlali_gated_scan(_ptr(a), _ptr(coef), _ptr(side), _i(side_stride), _ptr(side_bias), _ptr(state),
+                                    _sz(state.shape[1]), _sz(state_off), _ptr(batch.seq_start), _ptr(batch.seq_slot),
+                                    _i(batch.sequences), _ptr(out), _i(_dtype_code(out)), _i(width), _stream()), "gated_scan")
+
+
+# ---- attention over a window that keeps the first tokens -------------------------------------------------------
+
+def conv_heads_prepare(proj, taps_w, state, conv_off, q_gain, k_gain, inv_freq, rot_dims, batch, kv, q_out, nq, nkv, d, vd,
+                       eps, write_cache=True):
+    """``kv``: the cache view (keys [page, nkv, page_size, d], values [..., vd], page table)."""
+    _need_cuda(proj, taps_w, state, q_gain, k_gain, inv_freq, kv.keys, kv.values, kv.page_table, q_out)
+    rows = proj.shape[0]
+    C = (nq + nkv) * d + nkv * vd
+    require(proj.dtype == torch.float32 and proj.shape[1] == C and taps_w.shape[0] == C and taps_w.dtype == torch.float32
+            and q_out.shape == (rows, nq * d) and kv.keys.shape[-1] == d and kv.values.shape[-1] == vd
+            and kv.keys.dtype == kv.values.dtype and (rot_dims == 0 or inv_freq.numel() == rot_dims // 2),
+            "conv_heads_prepare: shapes or dtypes do not fit")
+    _check(lib().citlali_conv_heads_prepare(
+        _ptr(proj), _i(C), _ptr(taps_w), _i(taps_w.shape[1]), _ptr(state), _sz(state.shape[1] if state is not None else 0),
+        _sz(conv_off), _ptr(q_gain), _ptr(k_gain), _ptr(inv_freq), _i(rot_dims), _ptr(batch.row_slot), _ptr(batch.row_pos),
+        _ptr(kv.page_table), _i(kv.page_table.shape[1]), _ptr(kv.keys), _ptr(kv.values), _i(_dtype_code(kv.keys)),
+        _i(kv.page_size), _ptr(q_out), _i(_dtype_code(q_out)), _i(rows), _i(nq), _i(nkv), _i(d), _i(vd), _f(eps),
+        _i(1 if write_cache else 0), _stream()), "conv_heads_prepare")
+
+
+def attention_window(q, kv, batch, out, nq, nkv, d, vd, window, keep_first, scale):
+    _need_cuda(q, kv.keys, kv.values, kv.page_table, out)
+    rows = q.shape[0]
+    require(q.shape == (rows, nq * d) and out.shape == (rows, nq * vd) and q.dtype == out.dtype,
+            "attention_window: shapes or dtypes do not fit")
+    longest = kv.page_table.shape[1] * kv.page_size          # a bound that no step's lengths change
+    max_keys = min(longest, window + keep_first) if window else longest
+    _check(lib().citlali_attention_window(
+        _ptr(q), _i(_dtype_code(q)), _ptr(kv.keys), _ptr(kv.values), _i(_dtype_code(kv.keys)), _ptr(kv.page_table),
+        _i(kv.page_table.shape[1]), _ptr(batch.row_slot), _ptr(batch.row_pos), _ptr(out), _i(rows), _i(nq), _i(nkv), _i(d),
+        _i(vd), _i(kv.page_size), _i(int(window or 0)), _i(int(keep_first or 0)), _i(max_keys), _f(scale), _stream()),
+        "attention_window")
+
+
+# ---- routed experts -----------------------------------------------------------------------------------------------
+
+def moe_route(logits, weights, groups, keep, top, chosen=None):
+    _need_cuda(logits, weights, chosen)
+    rows, E = logits.shape
+    require(logits.dtype == torch.float32 and weights.dtype == torch.float32 and weights.shape == logits.shape
+            and (chosen is None or (chosen.dtype == torch.int32 and chosen.shape == (rows, top))),
+            "moe_route: shapes or dtypes do not fit")
+    _check(lib().citlali_moe_route(_ptr(logits), _ptr(weights), _ptr(chosen), _i(rows), _i(E), _i(int(groups or 0)),
+                                   _i(int(keep or 0)), _i(top), _stream()), "moe_route")
+
+
+def moe_scale(act, weights, ff):
+    _need_cuda(act, weights)
+    rows, E = weights.shape
+    require(act.shape == (rows, E * ff) and weights.dtype == torch.float32, "moe_scale: shapes or dtypes do not fit")
+    _check(lib().citlali_moe_scale(_ptr(act), _i(_dtype_code(act)), _ptr(weights), _i(rows), _i(E), _i(ff), _stream()),
+           "moe_scale")
 
 
 # ---- attention through a shared latent -------------------------------------------------------------

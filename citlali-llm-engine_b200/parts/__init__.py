@@ -10,3 +10,11 @@ from .latent import LatentAttention
 from .linear import DenseLinear
 from .norm import RMSNorm
 from .rotary import NoPosition, RotaryHalfSplit
+from . import ssm, recurrent, window_attention, parallel, moe   # more built-in parts
+from .block import SublayerOutputNormBlock
+from .moe import RoutedExperts
+from .norm import LayerNorm
+from .parallel import ParallelMixers
+from .recurrent import GatedRecurrentMixer
+from .ssm import StateSpaceMixer
+from .window_attention import WindowAttention

@@ -119,6 +119,10 @@ class StepBatch:
     # block to do together with its first read (one pass over the streams instead of two); the model does what is left
     # after the last layer.
     stream_write: Optional[tuple] = None
+    # A block whose last kernel also left the residual rows in the compute dtype hands them to the next block here
+    # (``rows_carry`` -> ``rows_carry_in``, moved by the model like ``norm_carry``).
+    rows_carry: Optional[torch.Tensor] = None
+    rows_carry_in: Optional[torch.Tensor] = None
 
     @property
     def rows(self) -> int:

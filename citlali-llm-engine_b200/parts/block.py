@@ -90,4 +90,63 @@ class PreNormResidualBlock:
         return x
 
 
+class SublayerOutputNormBlock:
+    """x += norm(mixer(x)); x += norm(feed_forward(x)): the sub-layers read the residual stream itself and the norm sits on
+    what they give.  Parts by name: ``mixer``, ``mixer_norm``, ``feed_forward``, ``feed_forward_norm`` (either pair may be
+    absent); a norm here is one with ``add_into(y, x, emit)`` (a layer norm).  The sub-layers' outputs are float32 and the
+    sum is a 32-bit addition; the rows a sub-layer reads are the residual rounded once to the compute dtype, left behind by
+    the kernel that did the sum before (for a model's first layer by a conversion of its own; none in the 32-bit path, where
+    the sub-layers read the residual's own memory).  Any registered mixer or feed-forward serves: one that says
+    ``can_overwrite`` stores its output, any other adds it into a zeroed buffer."""
+
+    def __init__(self, layer_spec):
+        has = layer_spec.parts.__contains__
+        self.subs = []
+        for role, norm_name in (("mixer", "mixer_norm"), ("feed_forward", "feed_forward_norm")):
+            if has(role):
+                norm = build_part("norm", layer_spec.part(norm_name))
+                if not callable(getattr(norm, "add_into", None)):
+                    raise TypeError(f"the norm behind a {role} must offer add_into(y, x, emit); '{layer_spec.part(norm_name).kind}' does not")
+                self.subs.append((role, build_part(role, layer_spec.part(role)), norm))
+        self.mixer = next((p for r, p, _ in self.subs if r == "mixer"), None)
+
+    def parts(self):
+        return [p for _, part, norm in self.subs for p in (part, norm)]
+
+    def tensor_specs(self):
+        return [t for p in self.parts() for t in p.tensor_specs()]
+
+    def cache_requirement(self):
+        return self.mixer.cache_requirement() if self.mixer is not None else None
+
+    def bind(self, weights, ctx):
+        for p in self.parts():
+            p.bind(weights, ctx)
+        self.dtype = ctx.dtype
+
+    def forward(self, x, batch, cache_view, write_cache=True):
+        rows, hidden = x.shape
+        h = batch.rows_carry_in if self.dtype != torch.float32 else x
+        if h is None or h.shape != x.shape or h.dtype != self.dtype:
+            h = torch.empty((rows, hidden), dtype=self.dtype, device=x.device)
+            ops.cast_rows(x, h)
+        for role, part, norm in self.subs:
+            fresh = bool(getattr(part, "can_overwrite", False))
+            y = (torch.empty if fresh else torch.zeros)((rows, hidden), dtype=torch.float32, device=x.device)
+            extra = {"overwrite": True} if fresh else {}
+            if role == "mixer":
+                part.forward(h, batch, cache_view, y, write_cache, **extra)
+            else:
+                part.forward(h, batch, y, **extra)
+            if self.dtype != torch.float32:
+                h = torch.empty((rows, hidden), dtype=self.dtype, device=x.device)
+                norm.add_into(y, x, emit=h)
+            else:
+                norm.add_into(y, x)
+        if self.dtype != torch.float32:
+            batch.rows_carry = h             # the residual as the next layer's sub-layers read it
+        return x
+
+
 register_part("block", "pre_norm_residual", PreNormResidualBlock)
+register_part("block", "sublayer_output_norm", SublayerOutputNormBlock)

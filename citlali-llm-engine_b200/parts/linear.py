@@ -133,3 +133,76 @@ class DenseLinear:
     @property
     def nbytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
+
+
+class BlockDiagonalLinear(DenseLinear):
+    """Several small maps with inputs of their own, run as one product: the matrices lie along the diagonal of one matrix
+    ``[sum out, sum in]`` whose other entries are zero, so ``x = [x_1 | x_2 | ...]`` gives ``y = [W_1 x_1 | W_2 x_2 | ...]``
+    in one launch (the second halves of low-rank maps, whose first halves were one stacked product)."""
+
+    def __init__(self, names: Sequence[str], shapes: Sequence[Sequence[int]]):
+        super().__init__(names, [int(o) for o, _ in shapes], sum(int(i) for _, i in shapes))
+        self.block_shapes = [(int(o), int(i)) for o, i in shapes]
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(n, s, "matrix") for n, s in zip(self.names, self.block_shapes)]
+
+    def bind(self, weights, ctx):
+        w = torch.zeros((self.out_features, self.in_features), dtype=ctx.dtype, device=ctx.device)
+        r = c = 0
+        for n, (o, i) in zip(self.names, self.block_shapes):
+            h = weights[n]
+            require(tuple(h.shape) == (o, i), f"unexpected tensor shape for {n}: got {list(h.shape)}, expected {[o, i]}")
+            h.copy_into(w[r:r + o, c:c + i])
+            r, c = r + o, c + i
+        self.weight = w
+        self.dtype = ctx.dtype
+        self.error_flag = ctx.error_flag
+
+
+class ExpertGateUp(DenseLinear):
+    """The gate and up matrices of E experts as one matrix ``[E * 2 * ff, in]``: expert after expert, within an expert
+    gate and up rows alternating in runs (of 16 where ff allows, for the product's gate epilogue; else of ff), so that the
+    gated activation comes out as ``[rows, E * ff]``, expert after expert."""
+
+    def __init__(self, gate_names: Sequence[str], up_names: Sequence[str], ff: int, in_features: int):
+        names = [n for pair in zip(gate_names, up_names) for n in pair]
+        super().__init__(names, [ff] * len(names), in_features)
+        self.experts, self.ff = len(gate_names), int(ff)
+        self.run = 16 if ff % 16 == 0 else int(ff)
+
+    def bind(self, weights, ctx):
+        E, ff, r = self.experts, self.ff, self.run
+        w = torch.empty((self.out_features, self.in_features), dtype=ctx.dtype, device=ctx.device)
+        runs = w.view(E, ff // r, 2, r, self.in_features)       # [expert, run, gate or up, row in run, in]
+        for k, n in enumerate(self.names):
+            h = weights[n]
+            require(tuple(h.shape) == (ff, self.in_features),
+                    f"unexpected tensor shape for {n}: got {list(h.shape)}, expected {[ff, self.in_features]}")
+            h.copy_into(runs[k // 2, :, k % 2])
+        self.weight = w
+        self.dtype = ctx.dtype
+        self.error_flag = ctx.error_flag
+
+
+class ExpertDown(DenseLinear):
+    """The output matrices of E experts side by side, ``[out, E * ff]``: applied to activations that were multiplied by
+    each expert's weight, one product gives the weighted sum of the experts' outputs."""
+
+    def __init__(self, names: Sequence[str], ff: int, out_features: int):
+        super().__init__(names, [out_features], len(names) * int(ff))
+        self.ff = int(ff)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(n, (self.out_features, self.ff), "matrix") for n in self.names]
+
+    def bind(self, weights, ctx):
+        w = torch.empty((self.out_features, self.in_features), dtype=ctx.dtype, device=ctx.device)
+        for e, n in enumerate(self.names):
+            h = weights[n]
+            require(tuple(h.shape) == (self.out_features, self.ff),
+                    f"unexpected tensor shape for {n}: got {list(h.shape)}, expected {[self.out_features, self.ff]}")
+            h.copy_into(w[:, e * self.ff:(e + 1) * self.ff])
+        self.weight = w
+        self.dtype = ctx.dtype
+        self.error_flag = ctx.error_flag

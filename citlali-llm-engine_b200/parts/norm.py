@@ -50,4 +50,37 @@ class RMSNorm:
         return out
 
 
+class LayerNorm:
+    """y = (x - mean) / sqrt(var + eps) * gain with var the mean of the squared deviations and no bias, over the hidden
+    size, in 32-bit.  ``forward`` norms rows of the residual stream (a model's last norm); ``add_into`` serves a block
+    whose norm sits on a sub-layer's output: ``x += norm(y)``, optionally leaving the updated rows in the compute dtype.
+
+    Parameters: size, eps; optional ``tensor`` (the gain's full name; default ``<prefix>.weight``)."""
+    graph_safe = True
+
+    def __init__(self, params, prefix: str):
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.name = str(params.get("tensor") or f"{prefix}.weight")
+        self.gain = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.size,), "gain")]
+
+    def bind(self, weights, ctx):
+        self.gain = bind_gain(weights, self.name, self.size, ctx)
+        self.dtype = ctx.dtype
+
+    def forward(self, x: torch.Tensor, row_index=None) -> torch.Tensor:
+        rows = x.shape[0] if row_index is None else row_index.numel()
+        out = torch.empty((rows, self.size), dtype=self.dtype, device=x.device)
+        ops.layer_norm_rows(x, self.gain, self.eps, out, row_index)
+        return out
+
+    def add_into(self, y: torch.Tensor, x: torch.Tensor, emit=None) -> torch.Tensor:
+        ops.layer_norm_add(y, self.gain, self.eps, x, emit)
+        return x
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "layer_norm", LayerNorm)
