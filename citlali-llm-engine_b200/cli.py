@@ -151,7 +151,15 @@ def print_model_info(model_path: str, out=sys.stdout) -> None:
     from .cache import KVRequirement, StateRequirement
     from .engine.model import cache_requirements_of
     kv = state = 0
-    for req in cache_requirements_of(spec):
+
+    def leaves(req):                     # a mixer made of several gives its requirements nested
+        if isinstance(req, (tuple, list)):
+            for r in req:
+                yield from leaves(r)
+        elif req is not None:
+            yield req
+
+    for req in (leaf for top in cache_requirements_of(spec) for leaf in leaves(top)):
         if isinstance(req, KVRequirement):
             kv += req.num_kv_heads * (req.head_dim + (req.head_dim if req.value_dim is None else req.value_dim))
         elif isinstance(req, StateRequirement):

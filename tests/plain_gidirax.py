@@ -74,7 +74,9 @@ def mamba2_mixer(h, w, p, m, eps):
     inner = H * P
     proj = h @ f64(w[p + ".in"]).T
     z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N:]
-    xbc = silu(causal_conv(xbc, w[p + ".conv"], w[p + ".conv.b"]))
+    if m.get("conv") is not None:                                 # a mixer without taps has no convolution
+        xbc = causal_conv(xbc, w[p + ".conv"], w[p + ".conv.b"])
+    xbc = silu(xbc)
     x = xbc[:, :inner].view(T, H, P)
     B = xbc[:, inner:inner + G * N].view(T, G, N)
     C = xbc[:, inner + G * N:].view(T, G, N)
@@ -131,7 +133,7 @@ def window_attention_mixer(h, w, p, m, eps):
         q = rotate_interleaved(q, rot["dims"], rot["base"])
         k = rotate_interleaved(k, rot["dims"], rot["base"])
     mask = m.get("mask") or {}
-    see = visible(T, mask.get("size"), mask.get("keep_first", 0))
+    see = visible(T, mask.get("size"), mask.get("keep_first") or 0)
     out = torch.zeros(T, H, V, dtype=F)
     for i in range(H):
         g = i // (H // G)
@@ -157,7 +159,9 @@ def recurrent_block_mixer(h, w, p, m, eps):
     T = h.shape[0]
     width, blocks = m["width"], m["blocks"]
     y = gelu_tanh(h @ f64(w[p + ".y"]).T + f64(w[p + ".y.b"])[None, :])
-    u = causal_conv(h @ f64(w[p + ".x"]).T + f64(w[p + ".x.b"])[None, :], w[p + ".conv"], w[p + ".conv.b"])
+    u = h @ f64(w[p + ".x"]).T + f64(w[p + ".x.b"])[None, :]
+    if m.get("conv") is not None:
+        u = causal_conv(u, w[p + ".conv"], w[p + ".conv.b"])
     ub = u.view(T, blocks, width // blocks)
     r = torch.sigmoid(torch.einsum("tbi,boi->tbo", ub, f64(w[p + ".ra"])) + f64(w[p + ".ra.b"])[None]).reshape(T, width)
     i = torch.sigmoid(torch.einsum("tbi,boi->tbo", ub, f64(w[p + ".ri"])) + f64(w[p + ".ri.b"])[None]).reshape(T, width)
@@ -170,7 +174,7 @@ def recurrent_block_mixer(h, w, p, m, eps):
 def parallel_mixer(h, w, p, m, eps):
     left = window_attention_mixer(h, w, p + ".left", m["left"], eps)
     right = recurrent_block_mixer(h, w, p + ".right", m["right"], eps)
-    return m["left_scale"] * left + m["right_scale"] * right
+    return m.get("left_scale", 1.0) * left + m.get("right_scale", 1.0) * right
 
 
 # ---- the delta rule with a decay per key channel -----------------------------------------------------------------------
