@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --workload 3|4 [--repetitions R]      the batch workloads of BASELINE.json's other shapes
-    python bench.py --design lanizen [--sizes small,medium,large]   another design beside Qwen3 at equal size
+    python bench.py --design lanizen|gidirax [--sizes small,medium,large]   a design beside another at equal size
 
 Prints ONE JSON line.  For each batch size (8, and 1 and 64 unless --skip-points) the run is a real one: the
 prompts (2,048 random tokens each) are prefilled in one step, then every sequence is decoded token by token up
@@ -318,8 +318,8 @@ class ClockSampler:
 
 
 def run_design(args):
-    """``--design``: a design beside the Qwen3 decoder at equal width, depth and parameter count (see
-    ``citlali_b200.measure``).  One JSON line; the default workload and its line are not touched."""
+    """``--design``: a design beside another of the library's at equal width and depth (Lanizen beside the Qwen3 decoder,
+    Gidirax beside Lanizen; see ``citlali_b200.measure``).  One JSON line; the default workload and its line are not touched."""
     import citlali_b200  # noqa: F401  (loads the package under its importable name)
     from citlali_b200 import measure
     sizes = [s for s in args.sizes.split(",") if s]
@@ -332,7 +332,8 @@ def run_design(args):
     result = measure.run(args.design, sizes, prompt_tokens=2048, batch=args.batch, context=2048,
                          steps=max(8, min(args.steps, 64)), warmup=max(args.warmup, 3))
     pk = peaks()
-    line = {"metric": f"{args.design} beside qwen3 at equal size: prompt and decode tokens/s", "design": args.design,
+    beside = measure.DESIGNS[args.design][1]
+    line = {"metric": f"{args.design} beside {beside} at equal size: prompt and decode tokens/s", "design": args.design,
             "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "peaks": pk, "sizes": result,
             "timing": "CUDA events; a 256 MB buffer is written between timed steps (L2 flushed); per-kernel times are "
                       "taken inside one step, each kernel between two events",
@@ -356,9 +357,9 @@ def main():
     ap.add_argument("--run-from", type=int, default=None,
                     help="length of the prompts of the decode runs (default: the prefill length, 2,048); close to the context "
                          "length it makes a short run, as a profiler capture needs")
-    ap.add_argument("--design", default=None, choices=["lanizen"],
-                    help="measure this design beside the Qwen3 decoder at equal sizes (prompt step, decode step, every "
-                         "kernel of both) instead of the benchmark configuration")
+    ap.add_argument("--design", default=None, choices=["lanizen", "gidirax"],
+                    help="measure this design beside the library's closest other design at equal sizes (prompt step, decode "
+                         "step, every kernel of both) instead of the benchmark configuration")
     ap.add_argument("--sizes", default="medium,large", help="with --design: which of small, medium, large")
     args = ap.parse_args()
 

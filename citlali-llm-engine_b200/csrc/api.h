@@ -85,13 +85,14 @@ void citlali_attention_decode_set_by_length(int on, int run_scale_q8);
 void citlali_attention_decode_set_per_warp(int on);
 
 // Causal attention of runs of new tokens (bfloat16, pages of 64) on the tensor cores.  Sequence b
-// owns rows seq_start[b] .. seq_start[b+1]-1 at positions seq_past[b] + i of slot seq_slot[b].
+// owns rows seq_start[b] .. seq_start[b+1]-1 at positions seq_past[b] + i of slot seq_slot[b].  window > 0: a row sees
+// its last `window` keys and the sequence's first `keep_first` keys.
 int citlali_attention_prefill_supports(int head_dim, int page_size);
 int citlali_attention_prefill(const void* q, int q_stride, const void* k_pool, const void* v_pool,
                               const int32_t* page_table, int page_table_stride,
                               const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_past,
                               void* out, int out_stride, int sequences, int max_new,
-                              int nq, int nkv, int head_dim, int page_size, int window, float scale,
+                              int nq, int nkv, int head_dim, int page_size, int window, int keep_first, float scale,
                               cudaStream_t stream);
 
 // The same on tcgen05 (scores and output in tensor memory), for head size 128 and pages of 64.

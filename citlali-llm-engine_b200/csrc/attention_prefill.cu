@@ -36,7 +36,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                          const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
                          const int32_t* __restrict__ seq_past,
                          __nv_bfloat16* __restrict__ out, int out_stride,
-                         int nq, int nkv, int window, float scale_log2) {
+                         int nq, int nkv, int window, int keep_first, float scale_log2) {
     constexpr int kRowBytes = D * 2 + 16;
     constexpr int kTileBytes = kTileK * kRowBytes;
     constexpr int kChunksPerRow = D / 8;                     // 16-byte pieces of a row
@@ -72,6 +72,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int first_pos = past + q0;
     const int lo_key = window > 0 ? max(0, first_pos - window + 1) : 0;
     const int tile_lo = lo_key / kTileK, tile_hi = last_pos / kTileK;
+    // with a window, the sequence's first keep_first keys stay visible: their tiles (those before the window's first) are
+    // walked first.  Walk index n stands for tile n up to kept_hi, then for tile_lo + (n - kept_hi - 1).
+    const int kept_hi = (window > 0 && keep_first > 0) ? min((keep_first - 1) / kTileK, tile_lo - 1) : -1;
+    const int walk_end = kept_hi + 1 + (tile_hi - tile_lo);          // the last walk index
+    auto tile_of = [&](int n) { return n <= kept_hi ? n : tile_lo + (n - kept_hi - 1); };
 
     auto load_tile = [&](int tile, int buf) {
         const size_t base = ((size_t)pages[tile] * nkv + g) * kTileK * D;
@@ -82,7 +87,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             cp_async16(s_v + buf * kTileBytes + r * kRowBytes + ch * 16, v_pool + src);
         }
     };
-    load_tile(tile_lo, 0);
+    load_tile(tile_of(0), 0);
     cp_async_commit();
 
     // Q fragments of this warp's 16 rows, for every 16-wide slice of the head
@@ -104,9 +109,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int pos0 = past + q0 + warp * 16 + (lane >> 2), pos1 = pos0 + 8;
     const int lo0 = window > 0 ? pos0 - window + 1 : 0, lo1 = window > 0 ? pos1 - window + 1 : 0;
 
-    for (int tile = tile_lo; tile <= tile_hi; ++tile) {
-        const int buf = (tile - tile_lo) & 1;
-        if (tile + 1 <= tile_hi) load_tile(tile + 1, buf ^ 1);
+    for (int n = 0; n <= walk_end; ++n) {
+        const int tile = tile_of(n);
+        const int buf = n & 1;
+        if (n + 1 <= walk_end) load_tile(tile_of(n + 1), buf ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
@@ -138,10 +144,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 #pragma unroll
             for (int i = 0; i < kTileK / 8; ++i) {
                 const int key = key_base + i * 8;
-                if (key > pos0 || key < lo0) s[i][0] = -INFINITY;
-                if (key + 1 > pos0 || key + 1 < lo0) s[i][1] = -INFINITY;
-                if (key > pos1 || key < lo1) s[i][2] = -INFINITY;
-                if (key + 1 > pos1 || key + 1 < lo1) s[i][3] = -INFINITY;
+                if (key > pos0 || (key < lo0 && key >= keep_first)) s[i][0] = -INFINITY;
+                if (key + 1 > pos0 || (key + 1 < lo0 && key + 1 >= keep_first)) s[i][1] = -INFINITY;
+                if (key > pos1 || (key < lo1 && key >= keep_first)) s[i][2] = -INFINITY;
+                if (key + 1 > pos1 || (key + 1 < lo1 && key + 1 >= keep_first)) s[i][3] = -INFINITY;
             }
         }
 #pragma unroll
@@ -205,8 +211,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 template <int D>
 static int launch(const void* q, int q_stride, const void* k_pool, const void* v_pool, const int32_t* page_table,
                   int page_table_stride, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_past,
-                  void* out, int out_stride, int sequences, int max_new, int nq, int nkv, int window, float scale,
-                  cudaStream_t stream) {
+                  void* out, int out_stride, int sequences, int max_new, int nq, int nkv, int window, int keep_first,
+                  float scale, cudaStream_t stream) {
     constexpr int smem = 5 * kTileK * (D * 2 + 16);
     auto kernel = attention_prefill_kernel<D>;
     static bool configured = false;
@@ -219,7 +225,7 @@ static int launch(const void* q, int q_stride, const void* k_pool, const void* v
     launch_kernel(kernel, grid, kWarps * 32, smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool,
                                                  (const __nv_bfloat16*)v_pool, page_table, page_table_stride, seq_start,
                                                  seq_slot, seq_past, (__nv_bfloat16*)out, out_stride, nq, nkv, window,
-                                                 scale * 1.4426950408889634f);
+                                                 window > 0 ? keep_first : 0, scale * 1.4426950408889634f);
     return CITLALI_LAUNCH_CHECK();
 }
 
@@ -239,14 +245,15 @@ extern "C" int citlali_attention_prefill_supports(int head_dim, int page_size) {
 
 // Attention of the new tokens of `sequences` sequences (bfloat16, pages of 64).  Sequence b owns
 // rows seq_start[b] .. seq_start[b+1]-1, at positions seq_past[b] + i of slot seq_slot[b];
-// `max_new` is the largest number of new tokens of any sequence.  The 64-bit row pitch of q
+// `max_new` is the largest number of new tokens of any sequence.  window > 0: only the last `window` keys and the
+// sequence's first `keep_first` keys are visible.  The 64-bit row pitch of q
 // (q_stride elements) and of out must keep rows 16-byte aligned.
 extern "C" int citlali_attention_prefill(const void* q, int q_stride, const void* k_pool, const void* v_pool,
                                          const int32_t* page_table, int page_table_stride,
                                          const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_past,
                                          void* out, int out_stride, int sequences, int max_new,
-                                         int nq, int nkv, int head_dim, int page_size, int window, float scale,
-                                         cudaStream_t stream) {
+                                         int nq, int nkv, int head_dim, int page_size, int window, int keep_first,
+                                         float scale, cudaStream_t stream) {
     if (sequences <= 0 || max_new <= 0) return 0;
     if (!citlali_attention_prefill_supports(head_dim, page_size)) {
         set_last_error("attention_prefill: no kernel for head size %d with pages of %d (head sizes 16..128 in steps of 16 "
@@ -262,7 +269,7 @@ extern "C" int citlali_attention_prefill(const void* q, int q_stride, const void
         return kBadAlignment;
     }
 #define CITLALI_FA(DD) case DD: return fa::launch<DD>(q, q_stride, k_pool, v_pool, page_table, page_table_stride, seq_start, \
-                                                      seq_slot, seq_past, out, out_stride, sequences, max_new, nq, nkv, window, scale, stream)
+                                                      seq_slot, seq_past, out, out_stride, sequences, max_new, nq, nkv, window, keep_first, scale, stream)
     switch (head_dim) {
         CITLALI_FA(16); CITLALI_FA(32); CITLALI_FA(48); CITLALI_FA(64); CITLALI_FA(80); CITLALI_FA(96); CITLALI_FA(112);
         CITLALI_FA(128); CITLALI_FA(256);

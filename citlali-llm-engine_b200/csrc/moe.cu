@@ -135,6 +135,29 @@ __global__ void moe_scale_kernel(T* __restrict__ act, const float* __restrict__ 
     }
 }
 
+// The same for bfloat16 rows whose experts' widths are multiples of 8: 16-byte words, each within one expert.
+__global__ void moe_scale_vec_kernel(__nv_bfloat16* __restrict__ act, const float* __restrict__ weights, int E, int ff) {
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.x;
+    const int words = E * ff / 8;
+    uint4* a = reinterpret_cast<uint4*>(act + (size_t)row * E * ff);
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < words; i += gridDim.y * blockDim.x) {
+        const float w = weights[(size_t)row * E + (i * 8) / ff];
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (w != 0.0f) {
+            v = a[i];
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(h[e]);
+                h[e] = __floats2bfloat162_rn(f.x * w, f.y * w);
+            }
+        }
+        a[i] = v;
+    }
+}
+
 }  // namespace citlali
 
 using namespace citlali;
@@ -156,6 +179,12 @@ extern "C" int citlali_moe_route(const float* logits, float* weights, int32_t* c
 
 extern "C" int citlali_moe_scale(void* act, int dtype, const float* weights, int rows, int E, int ff, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (dtype == kBF16 && ff % 8 == 0 && ((uintptr_t)act & 15u) == 0) {
+        const int by = (E * ff / 8 + 255) / 256;
+        dim3 grid(rows, by < 64 ? by : 64);
+        launch_kernel(moe_scale_vec_kernel, grid, 256, 0, stream, (__nv_bfloat16*)act, weights, E, ff);
+        return CITLALI_LAUNCH_CHECK();
+    }
     return CITLALI_DISPATCH_FLOAT(dtype, T, [&] {
         const int by = (E * ff + 255) / 256;
         dim3 grid(rows, by < 64 ? by : 64);

@@ -189,7 +189,7 @@ lru_gates_kernel(const float* __restrict__ u, const float* __restrict__ wa_t, co
 // S_t = a_t S_(t-1) + coef_t per channel, from and into state[slot][state_off + c]; out[row, c] = S_t *
 // gelu_tanh(side[row, c] + side_bias[c]), rounded once.  One thread a (sequence, channel), tokens in order.
 template <typename TO>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(32)
 gated_scan_kernel(const float* __restrict__ a, const float* __restrict__ coef, const float* __restrict__ side, int side_stride,
                   const float* __restrict__ side_bias, float* __restrict__ state, size_t state_stride, size_t state_off,
                   const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot, TO* __restrict__ out, int width) {
@@ -202,8 +202,25 @@ gated_scan_kernel(const float* __restrict__ a, const float* __restrict__ coef, c
     float* sp = state + (size_t)seq_slot[seq] * state_stride + state_off + c;
     float S = *sp;
     const float sb = side_bias ? side_bias[c] : 0.0f;
-#pragma unroll 4
-    for (int row = r0; row < r1; ++row) {
+    // eight tokens' inputs are fetched before the eight dependent steps that use them: a thread is alone with the latency
+    constexpr int AHEAD = 8;
+    int row = r0;
+    for (; row + AHEAD <= r1; row += AHEAD) {
+        float av[AHEAD], cv[AHEAD], sv[AHEAD];
+#pragma unroll
+        for (int j = 0; j < AHEAD; ++j) {
+            const size_t at = (size_t)(row + j) * width + c;
+            av[j] = a[at];
+            cv[j] = coef[at];
+            sv[j] = side[(size_t)(row + j) * side_stride + c];
+        }
+#pragma unroll
+        for (int j = 0; j < AHEAD; ++j) {
+            S = fmaf(av[j], S, cv[j]);
+            stf(out, (size_t)(row + j) * width + c, S * gelu_tanh_f(sv[j] + sb));
+        }
+    }
+    for (; row < r1; ++row) {
         const size_t at = (size_t)row * width + c;
         S = fmaf(a[at], S, coef[at]);
         stf(out, at, S * gelu_tanh_f(side[(size_t)row * side_stride + c] + sb));
@@ -308,13 +325,13 @@ extern "C" int citlali_gated_scan(const float* a, const float* coef, const float
                                   const int32_t* seq_slot, int sequences, void* out, int out_dtype, int width,
                                   cudaStream_t stream) {
     if (sequences <= 0 || width <= 0) return 0;
-    if ((width + 127) / 128 > 65535) {
+    if ((width + 31) / 32 > 65535) {
         set_last_error("gated_scan: a width of %d is too large", width);
         return kTooLarge;
     }
     return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {
-        dim3 grid(sequences, (width + 127) / 128);
-        launch_kernel(gated_scan_kernel<TO>, grid, 128, 0, stream, a, coef, side, side_stride, side_bias, state, state_stride,
+        dim3 grid(sequences, (width + 31) / 32);          // a warp a block: a sequence's channels spread over many SMs
+        launch_kernel(gated_scan_kernel<TO>, grid, 32, 0, stream, a, coef, side, side_stride, side_bias, state, state_stride,
                       state_off, seq_start, seq_slot, (TO*)out, width);
         return CITLALI_LAUNCH_CHECK();
     });

@@ -7,8 +7,10 @@
 //                        (2i, 2i+1) by position * inv_freq[i]; q goes to a buffer, k and v to the row's place in the
 //                        paged cache.  All float32 until the one rounding at the store.
 //   attention_window     one block a (row, query head): keys j <= pos with pos - j < window or j < keep_first (window 0:
-//                        every key); scores, softmax and the weighted sum in float32 in one fixed order, so a row's result
-//                        does not depend on the step it came in.
+//                        every key); scores, softmax and the weighted sum in float32.  The keys are dealt to 32 groups of
+//                        eight lanes by their place among the visible keys, each group keeps a running softmax of its own,
+//                        and the groups are merged in one fixed order: a row's result does not depend on the step it came
+//                        in, and no score is ever stored, so the number of keys has no limit.
 #include "api.h"
 #include "common.cuh"
 
@@ -103,58 +105,129 @@ conv_heads_prepare_kernel(const float* __restrict__ proj, int proj_stride, const
     }
 }
 
+// Eight lanes share a key: lane part p of them holds the key's (and the value's) elements p, p + 8, ... (or, for bfloat16
+// heads that are multiples of 8, the 16-byte pieces p, p + 8, ...).  A warp takes four keys at a time, a block's eight warps
+// the keys t = 4 warp + 32 i ...; every group of eight lanes keeps a running maximum, sum and weighted value sum of its own
+// keys (online softmax), and the 32 groups of the block are merged once at the end in group order.  Which keys a group gets
+// depends on the row's position, the window and the kept tokens alone.
+constexpr int kWinWarps = 8;
+constexpr int kWinMaxPerLane = 32;       // head sizes up to 256 over eight lanes
+
+template <typename T>
+__device__ __forceinline__ void load_slices(const T* __restrict__ row, int n, int part, bool vec, float (&x)[kWinMaxPerLane]) {
+    if constexpr (sizeof(T) == 2) {
+        if (vec) {                                             // pieces of 8 elements: part, part + 8, ...
+#pragma unroll
+            for (int c = 0; c < kWinMaxPerLane / 8; ++c) {
+                const int piece = part + 8 * c;
+                if (piece * 8 < n) {
+                    const uint4 w = *reinterpret_cast<const uint4*>(row + piece * 8);
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = __bfloat1622float2(h[e]);
+                        x[c * 8 + 2 * e] = f.x;
+                        x[c * 8 + 2 * e + 1] = f.y;
+                    }
+                }
+            }
+            return;
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < kWinMaxPerLane; ++c) {
+        const int i = part + 8 * c;
+        if (i < n) x[c] = ldf(row, i);
+    }
+}
+
+// the element of the head that slot c of a lane's slice stands for
+__device__ __forceinline__ int slice_element(int c, int part, bool vec) { return vec ? (part + 8 * (c >> 3)) * 8 + (c & 7) : part + 8 * c; }
+
 template <typename T, typename TQ>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kWinWarps * 32)
 attention_window_kernel(const TQ* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                         const int32_t* __restrict__ page_table, int table_stride, const int32_t* __restrict__ row_slot,
                         const int32_t* __restrict__ row_pos, TQ* __restrict__ out, int nq, int nkv, int d, int vd,
-                        int page_size, int window, int keep_first, float scale) {
-    extern __shared__ float smem[];
-    __shared__ float scratch[32];
+                        int page_size, int window, int keep_first, float scale, int vec) {
+    extern __shared__ float smem[];                            // [32 groups][vd] weighted sums, then [32] maxima, [32] sums
     dependents_may_launch();
     wait_for_predecessor();
     const int row = blockIdx.x, head = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int part = lane & 7, group = warp * 4 + (lane >> 3);
     const int g = head / (nq / nkv);
     const int pos = row_pos[row];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int first = min(keep_first, lo);                 // kept keys 0..first-1, then the window lo..pos
+    const int first = min(keep_first, lo);                     // kept keys 0..first-1, then the window lo..pos
     const int n = first + pos - lo + 1;
-    float* qs = smem;          // d
-    float* sc = smem + d;      // n
     const int32_t* pages = page_table + (size_t)row_slot[row] * table_stride;
-    const TQ* qrow = q + (size_t)row * nq * d + (size_t)head * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) qs[i] = ldf(qrow, i);
-    __syncthreads();
-    for (int t = warp; t < n; t += 4) {
-        const int key = t < first ? t : lo + (t - first);
-        const T* krow = k_pool + (((size_t)pages[key / page_size] * nkv + g) * page_size + key % page_size) * d;
-        float s = 0.0f;
-        for (int i = lane; i < d; i += 32) s = fmaf(qs[i], ldf(krow, i), s);
-        s = warp_sum(s);
-        if (lane == 0) sc[t] = s * scale;
-    }
-    __syncthreads();
-    float m = -INFINITY;
-    for (int t = threadIdx.x; t < n; t += blockDim.x) m = fmaxf(m, sc[t]);
-    m = block_max(m, scratch);
-    float z = 0.0f;
-    for (int t = threadIdx.x; t < n; t += blockDim.x) {
-        const float e = expf(sc[t] - m);
-        sc[t] = e;
-        z += e;
-    }
-    z = block_sum(z, scratch);
-    const float inv_z = 1.0f / z;
-    __syncthreads();
-    for (int i = threadIdx.x; i < vd; i += blockDim.x) {
-        float acc = 0.0f;
-        for (int t = 0; t < n; ++t) {
-            const int key = t < first ? t : lo + (t - first);
-            const T* vrow = v_pool + (((size_t)pages[key / page_size] * nkv + g) * page_size + key % page_size) * vd;
-            acc = fmaf(sc[t], ldf(vrow, i), acc);
+    const bool v8 = vec != 0;
+    float qs[kWinMaxPerLane], acc[kWinMaxPerLane];
+#pragma unroll
+    for (int c = 0; c < kWinMaxPerLane; ++c) { qs[c] = 0.0f; acc[c] = 0.0f; }
+    {
+        const TQ* qrow = q + (size_t)row * nq * d + (size_t)head * d;
+#pragma unroll
+        for (int c = 0; c < kWinMaxPerLane; ++c) {
+            const int i = slice_element(c, part, v8);
+            if (i < d) qs[c] = ldf(qrow, i) * scale;
         }
-        stf(out, (size_t)row * nq * vd + (size_t)head * vd + i, acc * inv_z);
+    }
+    float m = -INFINITY, l = 0.0f;
+    for (int base = warp * 4; base < n; base += kWinWarps * 4) {      // the same trips for all lanes of a warp
+        const int t = base + (lane >> 3);
+        const bool on = t < n;
+        const int key = t < first ? t : lo + (t - first);
+        const size_t at = on ? ((size_t)pages[key / page_size] * nkv + g) * page_size + key % page_size : 0;
+        float x[kWinMaxPerLane];
+#pragma unroll
+        for (int c = 0; c < kWinMaxPerLane; ++c) x[c] = 0.0f;
+        if (on) load_slices(k_pool + at * d, d, part, v8, x);
+        float s = 0.0f;
+#pragma unroll
+        for (int c = 0; c < kWinMaxPerLane; ++c) s = fmaf(qs[c], x[c], s);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        if (!on) continue;
+#pragma unroll
+        for (int c = 0; c < kWinMaxPerLane; ++c) x[c] = 0.0f;
+        load_slices(v_pool + at * vd, vd, part, v8, x);
+        if (s > m) {                                           // the group's maximum grows: what it has is scaled down
+            const float f = expf(m - s);                       // (zero the first time)
+            l *= f;
+#pragma unroll
+            for (int c = 0; c < kWinMaxPerLane; ++c) acc[c] *= f;
+            m = s;
+        }
+        const float p = expf(s - m);
+        l += p;
+#pragma unroll
+        for (int c = 0; c < kWinMaxPerLane; ++c) acc[c] = fmaf(p, x[c], acc[c]);
+    }
+    // the block's 32 groups, merged in group order
+    float* sums = smem;
+    float* gm = smem + 32 * vd;
+    float* gl = gm + 32;
+#pragma unroll
+    for (int c = 0; c < kWinMaxPerLane; ++c) {
+        const int i = slice_element(c, part, v8);
+        if (i < vd) sums[group * vd + i] = acc[c];
+    }
+    if (part == 0) { gm[group] = m; gl[group] = l; }
+    __syncthreads();
+    float top = -INFINITY;
+    for (int j = 0; j < 32; ++j) top = fmaxf(top, gm[j]);
+    for (int i = threadIdx.x; i < vd; i += blockDim.x) {
+        float z = 0.0f, a = 0.0f;
+        for (int j = 0; j < 32; ++j) {
+            if (gm[j] == -INFINITY) continue;                  // a group without keys
+            const float f = expf(gm[j] - top);
+            z = fmaf(f, gl[j], z);
+            a = fmaf(f, sums[j * vd + i], a);
+        }
+        stf(out, (size_t)row * nq * vd + (size_t)head * vd + i, a / z);
     }
 }
 
@@ -203,11 +276,14 @@ extern "C" int citlali_attention_window(const void* q, int q_dtype, const void* 
                        d, vd, window, keep_first);
         return kBadShape;
     }
-    const size_t smem = (size_t)(d + max_keys) * sizeof(float);
-    if (smem > 200 * 1024) {
-        set_last_error("attention_window: %d keys for one row need %zu bytes of shared memory, more than 204800", max_keys, smem);
+    (void)max_keys;
+    if (d > 8 * kWinMaxPerLane || vd > 8 * kWinMaxPerLane) {
+        set_last_error("attention_window: heads of %d (values %d) exceed %d", d, vd, 8 * kWinMaxPerLane);
         return kTooLarge;
     }
+    const size_t smem = (size_t)(32 * vd + 64) * sizeof(float);
+    // 16-byte pieces for bfloat16 heads that are multiples of 8 (rows of the pools then start on 16-byte boundaries)
+    const int vec = (cache_dtype == kBF16 && d % 8 == 0 && vd % 8 == 0 && ((uintptr_t)k_pool & 15u) == 0 && ((uintptr_t)v_pool & 15u) == 0) ? 1 : 0;
     return CITLALI_DISPATCH_FLOAT(cache_dtype, T, [&] {
         return CITLALI_DISPATCH_FLOAT(q_dtype, TQ, [&] {
             auto kernel = attention_window_kernel<T, TQ>;
@@ -216,8 +292,8 @@ extern "C" int citlali_attention_window(const void* q, int q_dtype, const void* 
                 if (e != cudaSuccess) return (int)e;
             }
             dim3 grid(rows, nq);
-            launch_kernel(kernel, grid, 128, smem, stream, (const TQ*)q, (const T*)k_pool, (const T*)v_pool, page_table,
-                          table_stride, row_slot, row_pos, (TQ*)out, nq, nkv, d, vd, page_size, window, keep_first, scale);
+            launch_kernel(kernel, grid, kWinWarps * 32, smem, stream, (const TQ*)q, (const T*)k_pool, (const T*)v_pool, page_table,
+                          table_stride, row_slot, row_pos, (TQ*)out, nq, nkv, d, vd, page_size, window, keep_first, scale, vec);
             return CITLALI_LAUNCH_CHECK();
         });
     });

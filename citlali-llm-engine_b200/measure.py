@@ -1,6 +1,7 @@
-"""Throughput of a decoder design beside the Qwen3 dense decoder at equal size, with every kernel of a step timed.
+"""Throughput of a decoder design beside another of the library's designs at equal size, with every kernel of a step timed.
 
-Used by ``bench.py --design lanizen``.  A size is a width and a number of layers; both models get that width, that
+Used by ``bench.py --design lanizen`` (beside the Qwen3 dense decoder) and ``--design gidirax`` (beside Lanizen, the
+closest design the library has: both mix delta-rule layers with windowed attention).  A size is a width and a number of layers; both models get that width, that
 many layers, feed-forwards of equal parameter count (8 width^2: two matrices of 4 width, or three of 8/3 width) and
 the same vocabulary, with random weights in bfloat16.  Measured per model: one prompt in one step (tokens a second),
 one decode step of ``batch`` sequences at ``context`` through the session's ``decode`` (the replayed graph where the
@@ -37,6 +38,27 @@ def lanizen_config(width: int, layers: int, vocab: int, streams: int = 4, window
     return config_from_dict({"architecture": "Lanizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
                              "embedding": {"scale": 1.0}, "streams": streams,
                              "layers": [latent if i % 4 == 3 else delta for i in range(layers)]})
+
+
+def gidirax_config(width: int, layers: int, vocab: int, window: int = 1024):
+    """Layers in turn: delta rule with a decay per key channel, state-space, attention beside a recurrent unit, delta rule.
+    Heads of 128 (state-space: heads of 64 over an inner width of 2 x width, a state of 128); sixteen experts of which a
+    token uses four, about 8 width^2 parameters in all experts of a layer."""
+    heads = max(1, width // 128)
+    ff = max(64, (width // 6 + 32) // 64 * 64)
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    delta = {"type": "channel_delta", "mlp": mlp,
+             "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64,
+                       "gate_rank": 64}}
+    ssm = {"type": "mamba2", "mlp": mlp,
+           "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4}}
+    par = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "conv": 4, "scale": 128 ** -0.5,
+                 "mask": {"size": window, "keep_first": 4}, "rot": {"base": 10000.0, "dims": 64}},
+        "right": {"width": width, "blocks": heads, "conv": 4}, "left_scale": 1.0, "right_scale": 1.0}}
+    order = [delta, ssm, par, delta]
+    return config_from_dict({"architecture": "Gidirax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+                             "layers": [order[i % 4] for i in range(layers)]})
 
 
 def qwen3_config(width: int, layers: int, vocab: int):
@@ -166,13 +188,18 @@ def measure_model(config, prompt_tokens: int, batch: int, context: int, steps: i
     return out
 
 
+DESIGNS = {"lanizen": (lanizen_config, "qwen3"), "gidirax": (gidirax_config, "lanizen"), "qwen3": (qwen3_config, None)}
+
+
 def run(design: str, sizes, prompt_tokens: int, batch: int, context: int, steps: int, warmup: int) -> dict:
+    """The design and the design it is held beside (``DESIGNS``), each at every size."""
+    make, beside = DESIGNS[design]
     result = {}
     for name in sizes:
         size = SIZES[name]
         result[name] = {
             "size": dict(size),
-            design: measure_model(lanizen_config(**size), prompt_tokens, batch, context, steps, warmup),
-            "qwen3": measure_model(qwen3_config(**size), prompt_tokens, batch, context, steps, warmup),
+            design: measure_model(make(**size), prompt_tokens, batch, context, steps, warmup),
+            beside: measure_model(DESIGNS[beside][0](**size), prompt_tokens, batch, context, steps, warmup),
         }
     return result

@@ -245,14 +245,15 @@ def attention(q, q_stride, cache_view, batch, out, nq, nkv, head_dim, window, sc
 
 
 def attention_prefill(q, q_stride, k_pool, v_pool, page_table, seq_start, seq_slot, seq_past, out, sequences, max_new,
-                      nq, nkv, head_dim, page_size, window, scale):
+                      nq, nkv, head_dim, page_size, window, scale, keep_first=0):
     _need_cuda(k_pool, v_pool, page_table, seq_start, seq_slot, seq_past, out)
     require(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
             "attention_prefill: bfloat16 only")
     _check(lib().citlali_attention_prefill(
         _ptr(q), _i(q_stride), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _i(page_table.shape[1]),
         _ptr(seq_start), _ptr(seq_slot), _ptr(seq_past), _ptr(out), _i(out.shape[1]), _i(sequences), _i(max_new),
-        _i(nq), _i(nkv), _i(head_dim), _i(page_size), _i(window or 0), _f(scale), _stream()), "attention_prefill")
+        _i(nq), _i(nkv), _i(head_dim), _i(page_size), _i(window or 0), _i(keep_first or 0), _f(scale), _stream()),
+        "attention_prefill")
 
 
 def attention_prefill_tc(q, q_stride, k_pool, v_pool, page_table, seq_start, seq_slot, seq_past, out, sequences, max_new,
@@ -708,10 +709,19 @@ def conv_heads_prepare(proj, taps_w, state, conv_off, q_gain, k_gain, inv_freq, 
 
 
 def attention_window(q, kv, batch, out, nq, nkv, d, vd, window, keep_first, scale):
+    """Attention of every row over its slot's cache, through a window that keeps the first tokens.  bfloat16 steps that
+    bring runs of tokens, with keys and values of one size the tensor-core kernel has, run that kernel; steps of single
+    tokens, the 32-bit path and other sizes run the kernel whose launch depends on the row count alone."""
     _need_cuda(q, kv.keys, kv.values, kv.page_table, out)
     rows = q.shape[0]
     require(q.shape == (rows, nq * d) and out.shape == (rows, nq * vd) and q.dtype == out.dtype,
             "attention_window: shapes or dtypes do not fit")
+    if (q.dtype == torch.bfloat16 and kv.keys.dtype == torch.bfloat16 and d == vd and not batch.is_decode
+            and (nq * d) % 8 == 0 and not torch.cuda.is_current_stream_capturing()
+            and lib().citlali_attention_prefill_supports(_i(d), _i(kv.page_size))):
+        attention_prefill(q, nq * d, kv.keys, kv.values, kv.page_table, batch.seq_start, batch.seq_slot, batch.seq_past, out,
+                          batch.sequences, batch.max_new, nq, nkv, d, kv.page_size, window, scale, keep_first=keep_first)
+        return
     longest = kv.page_table.shape[1] * kv.page_size          # a bound that no step's lengths change
     max_keys = min(longest, window + keep_first) if window else longest
     _check(lib().citlali_attention_window(

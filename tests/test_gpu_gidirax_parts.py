@@ -251,7 +251,14 @@ ATT = [dict(hidden_size=48, heads=4, kv_heads=2, dim=16, vdim=24, conv=3, qk_nor
        dict(hidden_size=32, heads=2, kv_heads=1, dim=24, vdim=40, conv=4, qk_norm_eps=1e-5, rot_dims=0, rot_base=1.0,
             scale=0.2, window=None, keep_first=0),
        dict(hidden_size=32, heads=2, kv_heads=2, dim=8, vdim=8, conv=2, qk_norm_eps=1e-5, rot_dims=4, rot_base=1e2,
-            scale=0.35, window=1, keep_first=70)]
+            scale=0.35, window=1, keep_first=70),
+       # keys and values of one size that the tensor-core kernel for runs of tokens takes (bfloat16)
+       dict(hidden_size=48, heads=4, kv_heads=2, dim=32, vdim=32, conv=2, qk_norm_eps=1e-5, rot_dims=16, rot_base=1e4,
+            scale=0.18, window=70, keep_first=3),
+       dict(hidden_size=32, heads=2, kv_heads=1, dim=16, vdim=16, conv=None, qk_norm_eps=1e-5, rot_dims=16, rot_base=1e3,
+            scale=0.25, window=9, keep_first=130),
+       dict(hidden_size=64, heads=2, kv_heads=2, dim=64, vdim=64, conv=3, qk_norm_eps=1e-6, rot_dims=32, rot_base=1e4,
+            scale=0.125, window=None, keep_first=0)]
 
 
 def attention_plain(params):
@@ -272,9 +279,10 @@ def test_window_attention_mixer(params, dtype):
     run_all_cuts("window_attention", params, attention_plain(params), dtype, T=150)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("decode_from", [None, 40])
-@pytest.mark.parametrize("window,keep_first", [(9, 2), (64, 4), (65, 1), (130, 0), (1, 3)])
-def test_window_edges_with_one_key_that_stands_out(window, keep_first, decode_from):
+@pytest.mark.parametrize("window,keep_first", [(9, 2), (64, 4), (65, 1), (130, 0), (1, 3), (20, 70)])
+def test_window_edges_with_one_key_that_stands_out(window, keep_first, decode_from, dtype):
     """Queries and keys are the inputs themselves (identity projections, no norm, no rotation, one tap); one key is made
     twenty times longer than the rest and every later query points along it, so a row's output is that key's value exactly
     when the key is visible: just inside and just outside the window, at the kept tokens' edge, over page borders."""
@@ -283,6 +291,7 @@ def test_window_edges_with_one_key_that_stands_out(window, keep_first, decode_fr
                   window=window, keep_first=keep_first)
     eye = torch.eye(d).to(torch.bfloat16)
     weights = {"m.q": eye, "m.k": eye, "m.v": eye, "m.o": eye}
+    # (in bfloat16 a prompt of this head size runs the tensor-core kernel for runs of tokens)
     for special in (0, keep_first - 1, keep_first, 63, 64, 100):
         if special < 0:
             continue
@@ -291,14 +300,14 @@ def test_window_edges_with_one_key_that_stands_out(window, keep_first, decode_fr
         h[:, 0] = 1.0                                       # every query has a part along the first axis ...
         h[special, 0] = 20.0                                # ... and one key is long along it
         h = h.to(torch.bfloat16).double()
-        hs = Harness("window_attention", params, torch.float32, weights=weights)
+        hs = Harness("window_attention", params, dtype, weights=weights)
         portions = [{"a": T}] if decode_from is None else [{"a": decode_from}] + [{"a": 1}] * (T - decode_from)
         got = hs.run({"a": h}, portions)["a"]
         see = plain.visible(T, window, keep_first)
         for i in range(T):
             s = (h[i] @ h[:i + 1].T).masked_fill(~see[i, :i + 1], -math.inf)
             ref = torch.softmax(s, -1) @ h[:i + 1]
-            assert float((got[i] - ref).abs().max()) < 1e-4, (window, keep_first, special, i)
+            assert float((got[i] - ref).abs().max()) < (1e-4 if dtype == torch.float32 else 0.15), (window, keep_first, special, i)
             if i > special:                                 # the test's point: the special key decides the row
                 visible_now = bool(see[i, special])
                 assert (float(got[i][0]) > 10.0) == visible_now, (window, keep_first, special, i)
