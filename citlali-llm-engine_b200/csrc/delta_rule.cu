@@ -26,16 +26,20 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-// A row's write strengths beta_h = sigmoid(row[beta_col + h]) and decays.  One decay a head: g_h = exp(-exp(a_log[h])
-// softplus(pre[h] + dt_bias[h])), pre = row[decay_col ...] or, if given, decay_row.  One a key channel (GD = D):
-// g_(h,i) = exp(-exp(a_log[h]) softplus(decay_row[h D + i] + dt_bias[h D + i])).  dst receives beta [H] | g [H GD].  All threads of the block take part.
+// Head h's write strength beta_h = sigmoid(row[beta_col + h]) and its decays, by the `threads` threads (this one is number
+// `tid` of them) that own the head's values.  One decay a head: g_h = exp(-exp(a_log[h]) softplus(pre[h] + dt_bias[h])),
+// pre = row[decay_col ...] or, if given, decay_row.  One a key channel (GD = D): g_(h,i) = exp(-exp(a_log[h])
+// softplus(decay_row[h D + i] + dt_bias[h D + i])).  dst receives beta [H] | g [H GD].
 __device__ __forceinline__ void write_strength_and_decay(const float* __restrict__ row, int beta_col, int decay_col,
                                                          const float* __restrict__ decay_row, const float* __restrict__ a_log,
-                                                         const float* __restrict__ dt_bias, float* __restrict__ dst, int H, int GD) {
-    for (int h = threadIdx.x; h < H; h += blockDim.x) dst[h] = sigmoidf_(row[beta_col + h]);
-    for (int i = threadIdx.x; i < H * GD; i += blockDim.x) {
+                                                         const float* __restrict__ dt_bias, float* __restrict__ dst, int H, int GD,
+                                                         int h, int tid, int threads) {
+    if (tid == 0) dst[h] = sigmoidf_(row[beta_col + h]);
+    const float rate = expf(a_log[h]);
+    for (int j = tid; j < GD; j += threads) {
+        const int i = h * GD + j;
         const float pre = decay_row ? decay_row[i] : row[decay_col + i];
-        dst[H + i] = expf(-expf(a_log[i / GD]) * softplusf_(pre + dt_bias[i]));
+        dst[H + i] = expf(-rate * softplusf_(pre + dt_bias[i]));
     }
 }
 
@@ -56,9 +60,10 @@ delta_prepare_kernel(const float* __restrict__ proj, int proj_stride, const floa
     const int C = 2 * KH * D + H * V;
     const int GD = channel_decay ? D : 1;                          // decays a head: one, or one a key channel
     float* dst = prep + (size_t)row * (C + H + H * GD);
-    if (blockIdx.y == 0) write_strength_and_decay(proj + (size_t)row * proj_stride, beta_col, decay_col,
-                                                  decay_in ? decay_in + (size_t)row * decay_stride : nullptr, a_log, dt_bias,
-                                                  dst + C, H, GD);
+    if (seg >= 2 * KH && seg < 2 * KH + H)
+        write_strength_and_decay(proj + (size_t)row * proj_stride, beta_col, decay_col,
+                                 decay_in ? decay_in + (size_t)row * decay_stride : nullptr, a_log, dt_bias, dst + C, H, GD,
+                                 seg - 2 * KH, lane, 32);
     if (seg >= 2 * KH + H) return;
     const bool unit = seg < 2 * KH;                           // q and k heads are made unit vectors
     const int c0 = unit ? seg * D : 2 * KH * D + (seg - 2 * KH) * V, n = unit ? D : V;
@@ -150,9 +155,10 @@ delta_prepare_block_kernel(const float* __restrict__ proj, int proj_stride, cons
     const int GD = channel_decay ? D : 1;
     float* dst = prep + (size_t)row * (C + H + H * GD);
     for (int i = threadIdx.x; i < n; i += blockDim.x) dst[c0 + i] = act[i] * f;      // a thread reads back what it wrote
-    if (seg == 0) write_strength_and_decay(proj + (size_t)row * proj_stride, beta_col, decay_col,
-                                           decay_in ? decay_in + (size_t)row * decay_stride : nullptr, a_log, dt_bias,
-                                           dst + C, H, GD);
+    if (seg >= 2 * KH)
+        write_strength_and_decay(proj + (size_t)row * proj_stride, beta_col, decay_col,
+                                 decay_in ? decay_in + (size_t)row * decay_stride : nullptr, a_log, dt_bias, dst + C, H, GD,
+                                 seg - 2 * KH, threadIdx.x, blockDim.x);
 }
 
 // After the step's rows were convolved: the sequence keeps its last taps-1 inputs.  One thread a channel.

@@ -113,7 +113,7 @@ ssm_prepare_kernel(const float* __restrict__ proj, int proj_stride, const float*
 // y = (o + D_h x) * silu(z), then divided by the root mean square of its norm group (`groups` equal parts of the row),
 // times the weight; rounded once.  One block a (row, group).
 template <typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 ssm_output_kernel(const float* __restrict__ o, const float* __restrict__ prep, int prep_stride, int x_col,
                   const float* __restrict__ proj, int proj_stride, const float* __restrict__ skip,
                   const float* __restrict__ weight, TO* __restrict__ y, int H, int P, int groups, float eps) {
@@ -141,17 +141,22 @@ ssm_output_kernel(const float* __restrict__ o, const float* __restrict__ prep, i
 // u [rows, width] is cut into `blocks` equal parts of bw; in part b:  r = sigmoid(Wa_b u_b + ba_b), i = sigmoid(Wi_b u_b +
 // bi_b), with the matrices given transposed [blocks, in, out] so that neighbouring threads read neighbouring words.
 //   log a = -8 r softplus(lam);  a = exp(log a);  coef = sqrt(1 - a^2) i u   (1 - a^2 = -expm1(2 log a)).
-// A block of the grid takes one part and RG rows; a thread one output channel (or several) for all of them.
+// A block of the grid takes one part, 32 of its output channels and kGateRows rows; its four warps split the part's inputs
+// into quarters (lane = output channel), and the four partial sums of an output meet in shared memory and are added in
+// quarter order: the order of a row's sums depends on the part's size alone.
 constexpr int kGateRows = 8;
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 lru_gates_kernel(const float* __restrict__ u, const float* __restrict__ wa_t, const float* __restrict__ ba,
                  const float* __restrict__ wi_t, const float* __restrict__ bi, const float* __restrict__ lam,
                  float* __restrict__ a_out, float* __restrict__ coef_out, int rows, int width, int bw) {
     extern __shared__ float us[];                             // [kGateRows][bw]
+    __shared__ float part_a[4][kGateRows][32], part_i[4][kGateRows][32];
     dependents_may_launch();
     wait_for_predecessor();
     const int b = blockIdx.y, r0 = blockIdx.x * kGateRows;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int o = blockIdx.z * 32 + lane;
     const int nr = min(kGateRows, rows - r0);
     for (int i = threadIdx.x; i < kGateRows * bw; i += blockDim.x) {
         const int r = i / bw, k = i % bw;
@@ -160,11 +165,14 @@ lru_gates_kernel(const float* __restrict__ u, const float* __restrict__ wa_t, co
     __syncthreads();
     const float* wa = wa_t + (size_t)b * bw * bw;
     const float* wi = wi_t + (size_t)b * bw * bw;
-    for (int o = threadIdx.x; o < bw; o += blockDim.x) {
-        float ra[kGateRows], ri[kGateRows];
+    const int quarter = (bw + 3) / 4;
+    const int k0 = warp * quarter, k1 = min(bw, k0 + quarter);
+    float ra[kGateRows], ri[kGateRows];
 #pragma unroll
-        for (int r = 0; r < kGateRows; ++r) { ra[r] = ba[b * bw + o]; ri[r] = bi[b * bw + o]; }
-        for (int k = 0; k < bw; ++k) {
+    for (int r = 0; r < kGateRows; ++r) { ra[r] = 0.0f; ri[r] = 0.0f; }
+    if (o < bw) {
+#pragma unroll 4
+        for (int k = k0; k < k1; ++k) {
             const float a = wa[(size_t)k * bw + o], c = wi[(size_t)k * bw + o];
 #pragma unroll
             for (int r = 0; r < kGateRows; ++r) {
@@ -173,16 +181,19 @@ lru_gates_kernel(const float* __restrict__ u, const float* __restrict__ wa_t, co
                 ri[r] = fmaf(c, x, ri[r]);
             }
         }
-        const float sp = softplus_f(lam[b * bw + o]);
+    }
 #pragma unroll
-        for (int r = 0; r < kGateRows; ++r) {
-            if (r < nr) {
-                const float log_a = -8.0f * sigmoid_f(ra[r]) * sp;
-                const size_t at = (size_t)(r0 + r) * width + b * bw + o;
-                a_out[at] = expf(log_a);
-                coef_out[at] = sqrtf(-expm1f(2.0f * log_a)) * sigmoid_f(ri[r]) * us[r * bw + o];
-            }
-        }
+    for (int r = 0; r < kGateRows; ++r) { part_a[warp][r][lane] = ra[r]; part_i[warp][r][lane] = ri[r]; }
+    __syncthreads();
+    if (o >= bw) return;
+    const float sp = softplus_f(lam[b * bw + o]);
+    for (int r = warp; r < nr; r += 4) {                      // a warp finishes every fourth row
+        const float za = ((part_a[0][r][lane] + part_a[1][r][lane]) + part_a[2][r][lane]) + part_a[3][r][lane] + ba[b * bw + o];
+        const float zi = ((part_i[0][r][lane] + part_i[1][r][lane]) + part_i[2][r][lane]) + part_i[3][r][lane] + bi[b * bw + o];
+        const float log_a = -8.0f * sigmoid_f(za) * sp;
+        const size_t at = (size_t)(r0 + r) * width + b * bw + o;
+        a_out[at] = expf(log_a);
+        coef_out[at] = sqrtf(-expm1f(2.0f * log_a)) * sigmoid_f(zi) * us[r * bw + o];
     }
 }
 
@@ -294,7 +305,8 @@ extern "C" int citlali_ssm_output(const float* o, const float* prep, int prep_st
     }
     return CITLALI_DISPATCH_FLOAT(y_dtype, TO, [&] {
         dim3 grid(rows, groups);
-        launch_kernel(ssm_output_kernel<TO>, grid, 256, 0, stream, o, prep, prep_stride, x_col, proj, proj_stride, skip, weight,
+        const int threads = (H * P) / groups >= 4096 ? 1024 : 256;       // by the group's size alone: one order of sums
+        launch_kernel(ssm_output_kernel<TO>, grid, threads, 0, stream, o, prep, prep_stride, x_col, proj, proj_stride, skip, weight,
                       (TO*)y, H, P, groups, eps);
         return CITLALI_LAUNCH_CHECK();
     });
@@ -314,9 +326,8 @@ extern "C" int citlali_lru_gates(const float* u, const float* wa_t, const float*
         set_last_error("lru_gates: gate blocks of %d channels exceed the kernel's 1536", bw);
         return kTooLarge;
     }
-    dim3 grid((rows + kGateRows - 1) / kGateRows, blocks);
-    const int threads = bw >= 256 ? 256 : ((bw + 31) / 32) * 32;
-    launch_kernel(lru_gates_kernel, grid, threads, smem, stream, u, wa_t, ba, wi_t, bi, lam, a_out, coef_out, rows, width, bw);
+    dim3 grid((rows + kGateRows - 1) / kGateRows, blocks, (bw + 31) / 32);
+    launch_kernel(lru_gates_kernel, grid, 128, smem, stream, u, wa_t, ba, wi_t, bi, lam, a_out, coef_out, rows, width, bw);
     return CITLALI_LAUNCH_CHECK();
 }
 

@@ -71,6 +71,92 @@ layer_norm_rows_kernel(const float* __restrict__ x, const TG* __restrict__ gain,
         stf(out, (size_t)row * hidden + i, (row_s[i] - mean) * inv * ldf(gain, i));
 }
 
+// The same two kernels for rows that are multiples of 4 and at most 8192 elements: a thread keeps its part of the row in
+// registers (two 16-byte words at most), so the row is read once with 16-byte loads; few rows get up to 1024 threads each.
+template <typename TE>
+__device__ __forceinline__ void store4(TE* p, size_t at, const float4& v) {
+    if constexpr (sizeof(TE) == 2) {
+        uint2 w;
+        *reinterpret_cast<__nv_bfloat162*>(&w.x) = __floats2bfloat162_rn(v.x, v.y);
+        *reinterpret_cast<__nv_bfloat162*>(&w.y) = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2*>(p + at) = w;
+    } else {
+        *reinterpret_cast<float4*>(p + at) = v;
+    }
+}
+template <typename TG>
+__device__ __forceinline__ float4 load4(const TG* p, size_t at) {
+    if constexpr (sizeof(TG) == 2) {
+        const uint2 w = *reinterpret_cast<const uint2*>(p + at);
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.y));
+        return make_float4(lo.x, lo.y, hi.x, hi.y);
+    } else {
+        return *reinterpret_cast<const float4*>(p + at);
+    }
+}
+
+// ADD: x += norm(y) and emit; otherwise out = norm(x[index]).
+template <typename TG, typename TO, bool ADD>
+__global__ void __launch_bounds__(1024)
+layer_norm_vec_kernel(const float* __restrict__ src_rows, const TG* __restrict__ gain, const int32_t* __restrict__ row_index,
+                      float* __restrict__ x, TO* __restrict__ out, int hidden, float eps) {
+    __shared__ float scratch[32];
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.x;
+    const float* src = src_rows + (size_t)((!ADD && row_index) ? row_index[row] : row) * hidden;
+    const int quads = hidden >> 2;
+    float4 v[2];
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int qd = threadIdx.x + j * blockDim.x;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (qd < quads) v[j] = *reinterpret_cast<const float4*>(src + qd * 4);
+        s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    }
+    const float mean = block_sum(s, scratch) / (float)hidden;
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int qd = threadIdx.x + j * blockDim.x;
+        if (qd < quads) {
+            v[j].x -= mean; v[j].y -= mean; v[j].z -= mean; v[j].w -= mean;
+            ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss); ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+        }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int qd = threadIdx.x + j * blockDim.x;
+        if (qd < quads) {
+            const float4 g = load4(gain, (size_t)qd * 4);
+            float4 r = make_float4(v[j].x * inv * g.x, v[j].y * inv * g.y, v[j].z * inv * g.z, v[j].w * inv * g.w);
+            const size_t at = (size_t)row * hidden + qd * 4;
+            if (ADD) {
+                const float4 old = *reinterpret_cast<const float4*>(x + at);
+                r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
+                *reinterpret_cast<float4*>(x + at) = r;
+                if (out) store4(out, at, r);
+            } else {
+                store4(out, at, r);
+            }
+        }
+    }
+}
+
+// threads a row for the kernel above: one 16-byte word a thread up to 1024 threads.  The number follows the row's length
+// alone, so a row's sums are taken in one order whatever the step's size.
+static int vec_threads(int rows, int hidden) {
+    (void)rows;
+    int t = ((hidden / 4 + 31) / 32) * 32;
+    return t < 32 ? 32 : (t > 1024 ? 1024 : t);
+}
+static bool vec_ok(int hidden, const void* a, const void* b, const void* c, const void* d) {
+    return hidden % 4 == 0 && hidden <= 8192 && (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c | (uintptr_t)d) & 15u) == 0;
+}
+
 template <typename TO>
 __global__ void cast_rows_kernel(const float* __restrict__ x, TO* __restrict__ out, size_t n) {
     dependents_may_launch();
@@ -103,6 +189,15 @@ extern "C" int citlali_layer_norm_add(const float* y, const void* gain, int gain
         set_last_error("layer_norm_add: rows of %d elements do not fit a block's shared memory", hidden);
         return kTooLarge;
     }
+    if (vec_ok(hidden, y, gain, x, emit)) {
+        return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
+            return CITLALI_DISPATCH_FLOAT(emit_dtype, TE, [&] {
+                launch_kernel(layer_norm_vec_kernel<TG, TE, true>, rows, vec_threads(rows, hidden), 0, stream, y, (const TG*)gain,
+                              (const int32_t*)nullptr, x, (TE*)emit, hidden, eps);
+                return CITLALI_LAUNCH_CHECK();
+            });
+        });
+    }
     return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
         return CITLALI_DISPATCH_FLOAT(emit_dtype, TE, [&] {
             auto kernel = layer_norm_add_kernel<TG, TE>;
@@ -123,6 +218,15 @@ extern "C" int citlali_layer_norm_rows(const float* x, const void* gain, int gai
     if (hidden <= 0 || smem > 200 * 1024) {
         set_last_error("layer_norm_rows: rows of %d elements do not fit a block's shared memory", hidden);
         return kTooLarge;
+    }
+    if (vec_ok(hidden, x, gain, out, nullptr)) {
+        return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
+            return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {
+                launch_kernel(layer_norm_vec_kernel<TG, TO, false>, rows, vec_threads(rows, hidden), 0, stream, x, (const TG*)gain,
+                              row_index, (float*)nullptr, (TO*)out, hidden, eps);
+                return CITLALI_LAUNCH_CHECK();
+            });
+        });
     }
     return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
         return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {

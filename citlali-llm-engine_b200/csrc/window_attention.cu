@@ -111,45 +111,33 @@ conv_heads_prepare_kernel(const float* __restrict__ proj, int proj_stride, const
 // keys (online softmax), and the 32 groups of the block are merged once at the end in group order.  Which keys a group gets
 // depends on the row's position, the window and the kept tokens alone.
 constexpr int kWinWarps = 8;
-constexpr int kWinMaxPerLane = 32;       // head sizes up to 256 over eight lanes
 
-template <typename T>
-__device__ __forceinline__ void load_slices(const T* __restrict__ row, int n, int part, bool vec, float (&x)[kWinMaxPerLane]) {
-    if constexpr (sizeof(T) == 2) {
-        if (vec) {                                             // pieces of 8 elements: part, part + 8, ...
+// PL: elements of a head a lane holds (heads up to 8 PL).  VEC: bfloat16 pools and head sizes that are multiples of 8; a lane
+// then holds the 16-byte pieces part, part + 8, ..., and the keys of two or four turns are fetched before any of them is used
+// (a group of lanes is alone with the latency of its loads; two blocks share an SM for heads up to 128).
+template <int PL>
+__device__ __forceinline__ int slice_element(int c, int part, bool vec) { return vec ? (part + 8 * (c >> 3)) * 8 + (c & 7) : part + 8 * c; }
+
+template <int PL>
+__device__ __forceinline__ void unpack_pieces(const uint4 (&raw)[PL / 8 > 0 ? PL / 8 : 1], float (&x)[PL]) {
 #pragma unroll
-            for (int c = 0; c < kWinMaxPerLane / 8; ++c) {
-                const int piece = part + 8 * c;
-                if (piece * 8 < n) {
-                    const uint4 w = *reinterpret_cast<const uint4*>(row + piece * 8);
-                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+    for (int c = 0; c < PL / 8; ++c) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[c]);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 f = __bfloat1622float2(h[e]);
-                        x[c * 8 + 2 * e] = f.x;
-                        x[c * 8 + 2 * e + 1] = f.y;
-                    }
-                }
-            }
-            return;
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            x[c * 8 + 2 * e] = f.x;
+            x[c * 8 + 2 * e + 1] = f.y;
         }
-    }
-#pragma unroll
-    for (int c = 0; c < kWinMaxPerLane; ++c) {
-        const int i = part + 8 * c;
-        if (i < n) x[c] = ldf(row, i);
     }
 }
 
-// the element of the head that slot c of a lane's slice stands for
-__device__ __forceinline__ int slice_element(int c, int part, bool vec) { return vec ? (part + 8 * (c >> 3)) * 8 + (c & 7) : part + 8 * c; }
-
-template <typename T, typename TQ>
-__global__ void __launch_bounds__(kWinWarps * 32)
+template <typename T, typename TQ, int PL, bool VEC>
+__global__ void __launch_bounds__(kWinWarps * 32, PL <= 16 ? 2 : 1)
 attention_window_kernel(const TQ* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                         const int32_t* __restrict__ page_table, int table_stride, const int32_t* __restrict__ row_slot,
                         const int32_t* __restrict__ row_pos, TQ* __restrict__ out, int nq, int nkv, int d, int vd,
-                        int page_size, int window, int keep_first, float scale, int vec) {
+                        int page_size, int window, int keep_first, float scale) {
     extern __shared__ float smem[];                            // [32 groups][vd] weighted sums, then [32] maxima, [32] sums
     dependents_may_launch();
     wait_for_predecessor();
@@ -162,57 +150,99 @@ attention_window_kernel(const TQ* __restrict__ q, const T* __restrict__ k_pool, 
     const int first = min(keep_first, lo);                     // kept keys 0..first-1, then the window lo..pos
     const int n = first + pos - lo + 1;
     const int32_t* pages = page_table + (size_t)row_slot[row] * table_stride;
-    const bool v8 = vec != 0;
-    float qs[kWinMaxPerLane], acc[kWinMaxPerLane];
+    float qs[PL], acc[PL];
 #pragma unroll
-    for (int c = 0; c < kWinMaxPerLane; ++c) { qs[c] = 0.0f; acc[c] = 0.0f; }
-    {
-        const TQ* qrow = q + (size_t)row * nq * d + (size_t)head * d;
-#pragma unroll
-        for (int c = 0; c < kWinMaxPerLane; ++c) {
-            const int i = slice_element(c, part, v8);
-            if (i < d) qs[c] = ldf(qrow, i) * scale;
-        }
+    for (int c = 0; c < PL; ++c) {
+        const int i = slice_element<PL>(c, part, VEC);
+        qs[c] = i < d ? ldf(q + (size_t)row * nq * d + (size_t)head * d, i) * scale : 0.0f;
+        acc[c] = 0.0f;
     }
     float m = -INFINITY, l = 0.0f;
-    for (int base = warp * 4; base < n; base += kWinWarps * 4) {      // the same trips for all lanes of a warp
-        const int t = base + (lane >> 3);
-        const bool on = t < n;
-        const int key = t < first ? t : lo + (t - first);
-        const size_t at = on ? ((size_t)pages[key / page_size] * nkv + g) * page_size + key % page_size : 0;
-        float x[kWinMaxPerLane];
-#pragma unroll
-        for (int c = 0; c < kWinMaxPerLane; ++c) x[c] = 0.0f;
-        if (on) load_slices(k_pool + at * d, d, part, v8, x);
-        float s = 0.0f;
-#pragma unroll
-        for (int c = 0; c < kWinMaxPerLane; ++c) s = fmaf(qs[c], x[c], s);
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        if (!on) continue;
-#pragma unroll
-        for (int c = 0; c < kWinMaxPerLane; ++c) x[c] = 0.0f;
-        load_slices(v_pool + at * vd, vd, part, v8, x);
-        if (s > m) {                                           // the group's maximum grows: what it has is scaled down
+    auto take = [&](float s, const float (&v)[PL]) {           // one key's score and value into the group's running softmax
+        if (s > m) {                                           // the maximum grows: what the group has is scaled down
             const float f = expf(m - s);                       // (zero the first time)
             l *= f;
 #pragma unroll
-            for (int c = 0; c < kWinMaxPerLane; ++c) acc[c] *= f;
+            for (int c = 0; c < PL; ++c) acc[c] *= f;
             m = s;
         }
         const float p = expf(s - m);
         l += p;
 #pragma unroll
-        for (int c = 0; c < kWinMaxPerLane; ++c) acc[c] = fmaf(p, x[c], acc[c]);
+        for (int c = 0; c < PL; ++c) acc[c] = fmaf(p, v[c], acc[c]);
+    };
+    auto place = [&](int t) -> size_t {                        // where the t-th visible key lies in the pools (in rows)
+        const int key = t < first ? t : lo + (t - first);
+        return ((size_t)pages[key / page_size] * nkv + g) * page_size + key % page_size;
+    };
+    constexpr int STEP = kWinWarps * 4;                        // keys the block takes a turn
+    if constexpr (VEC) {
+        constexpr int U = PL <= 8 ? 4 : 2, W = PL / 8;       // keys in flight a group: as many as two blocks' registers allow
+        for (int base = warp * 4; base < n; base += STEP * U) {        // the same trips for all lanes of a warp
+            uint4 kr[U][W], vr[U][W];
+            bool on[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int t = base + u * STEP + (lane >> 3);
+                on[u] = t < n;
+                const size_t at = on[u] ? place(t) : 0;
+#pragma unroll
+                for (int c = 0; c < W; ++c) {
+                    const int piece = part + 8 * c;
+                    kr[u][c] = (on[u] && piece * 8 < d) ? *reinterpret_cast<const uint4*>(k_pool + at * d + piece * 8) : make_uint4(0, 0, 0, 0);
+                    vr[u][c] = (on[u] && piece * 8 < vd) ? *reinterpret_cast<const uint4*>(v_pool + at * vd + piece * 8) : make_uint4(0, 0, 0, 0);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (base + u * STEP >= n) break;               // (warp-uniform) no lane of the warp has a key in this turn
+                float x[PL];
+                unpack_pieces<PL>(kr[u], x);
+                float s = 0.0f;
+#pragma unroll
+                for (int c = 0; c < PL; ++c) s = fmaf(qs[c], x[c], s);
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                s += __shfl_xor_sync(0xffffffffu, s, 4);
+                if (on[u]) {
+                    unpack_pieces<PL>(vr[u], x);
+                    take(s, x);
+                }
+            }
+        }
+    } else {
+        for (int base = warp * 4; base < n; base += STEP) {
+            const int t = base + (lane >> 3);
+            const bool on = t < n;
+            const size_t at = on ? place(t) : 0;
+            float x[PL];
+            float s = 0.0f;
+#pragma unroll
+            for (int c = 0; c < PL; ++c) {
+                const int i = part + 8 * c;
+                x[c] = (on && i < d) ? ldf(k_pool, at * d + i) : 0.0f;
+                s = fmaf(qs[c], x[c], s);
+            }
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            if (on) {
+#pragma unroll
+                for (int c = 0; c < PL; ++c) {
+                    const int i = part + 8 * c;
+                    x[c] = i < vd ? ldf(v_pool, at * vd + i) : 0.0f;
+                }
+                take(s, x);
+            }
+        }
     }
     // the block's 32 groups, merged in group order
     float* sums = smem;
     float* gm = smem + 32 * vd;
     float* gl = gm + 32;
 #pragma unroll
-    for (int c = 0; c < kWinMaxPerLane; ++c) {
-        const int i = slice_element(c, part, v8);
+    for (int c = 0; c < PL; ++c) {
+        const int i = slice_element<PL>(c, part, VEC);
         if (i < vd) sums[group * vd + i] = acc[c];
     }
     if (part == 0) { gm[group] = m; gl[group] = l; }
@@ -229,6 +259,18 @@ attention_window_kernel(const TQ* __restrict__ q, const T* __restrict__ k_pool, 
         }
         stf(out, (size_t)row * nq * vd + (size_t)head * vd + i, a / z);
     }
+}
+
+template <typename T, typename TQ, int PL, bool VEC>
+static int launch_window(const void* q, const void* k_pool, const void* v_pool, const int32_t* page_table, int table_stride,
+                         const int32_t* row_slot, const int32_t* row_pos, void* out, int rows, int nq, int nkv, int d, int vd,
+                         int page_size, int window, int keep_first, float scale, cudaStream_t stream) {
+    const size_t smem = (size_t)(32 * vd + 64) * sizeof(float);
+    dim3 grid(rows, nq);
+    launch_kernel(attention_window_kernel<T, TQ, PL, VEC>, grid, kWinWarps * 32, smem, stream, (const TQ*)q, (const T*)k_pool,
+                  (const T*)v_pool, page_table, table_stride, row_slot, row_pos, (TQ*)out, nq, nkv, d, vd, page_size, window,
+                  keep_first, scale);
+    return CITLALI_LAUNCH_CHECK();
 }
 
 }  // namespace citlali
@@ -277,24 +319,28 @@ extern "C" int citlali_attention_window(const void* q, int q_dtype, const void* 
         return kBadShape;
     }
     (void)max_keys;
-    if (d > 8 * kWinMaxPerLane || vd > 8 * kWinMaxPerLane) {
-        set_last_error("attention_window: heads of %d (values %d) exceed %d", d, vd, 8 * kWinMaxPerLane);
+    const int big = d > vd ? d : vd;
+    if (big > 256) {
+        set_last_error("attention_window: heads of %d (values %d) exceed 256", d, vd);
         return kTooLarge;
     }
-    const size_t smem = (size_t)(32 * vd + 64) * sizeof(float);
-    // 16-byte pieces for bfloat16 heads that are multiples of 8 (rows of the pools then start on 16-byte boundaries)
-    const int vec = (cache_dtype == kBF16 && d % 8 == 0 && vd % 8 == 0 && ((uintptr_t)k_pool & 15u) == 0 && ((uintptr_t)v_pool & 15u) == 0) ? 1 : 0;
+    // 16-byte pieces for bfloat16 pools and heads that are multiples of 8 (rows of the pools then start on 16-byte boundaries)
+    const bool vec = cache_dtype == kBF16 && d % 8 == 0 && vd % 8 == 0 && ((uintptr_t)k_pool & 15u) == 0 && ((uintptr_t)v_pool & 15u) == 0;
+#define CITLALI_WINDOW(T, TQ)                                                                                             \
+    do {                                                                                                                  \
+        if (vec) {                                                                                                        \
+            if constexpr (sizeof(T) == 2) {                                                                               \
+                if (big <= 64) return launch_window<T, TQ, 8, true>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, stream); \
+                if (big <= 128) return launch_window<T, TQ, 16, true>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, stream); \
+                return launch_window<T, TQ, 32, true>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, stream); \
+            }                                                                                                             \
+        }                                                                                                                 \
+        if (big <= 64) return launch_window<T, TQ, 8, false>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, stream); \
+        if (big <= 128) return launch_window<T, TQ, 16, false>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, stream); \
+        return launch_window<T, TQ, 32, false>(q, k_pool, v_pool, page_table, table_stride, row_slot, row_pos, out, rows, nq, nkv, d, vd, page_size, window, keep_first, scale, stream); \
+    } while (0)
     return CITLALI_DISPATCH_FLOAT(cache_dtype, T, [&] {
-        return CITLALI_DISPATCH_FLOAT(q_dtype, TQ, [&] {
-            auto kernel = attention_window_kernel<T, TQ>;
-            if (smem > 48 * 1024) {
-                cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                if (e != cudaSuccess) return (int)e;
-            }
-            dim3 grid(rows, nq);
-            launch_kernel(kernel, grid, kWinWarps * 32, smem, stream, (const TQ*)q, (const T*)k_pool, (const T*)v_pool, page_table,
-                          table_stride, row_slot, row_pos, (TQ*)out, nq, nkv, d, vd, page_size, window, keep_first, scale, vec);
-            return CITLALI_LAUNCH_CHECK();
-        });
+        return CITLALI_DISPATCH_FLOAT(q_dtype, TQ, [&]() -> int { CITLALI_WINDOW(T, TQ); });
     });
+#undef CITLALI_WINDOW
 }
