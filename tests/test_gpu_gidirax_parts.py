@@ -314,6 +314,29 @@ def test_window_edges_with_one_key_that_stands_out(window, keep_first, decode_fr
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window,keep_first", [(None, 0), (40, 6)])
+def test_a_far_key_among_hundreds(window, keep_first, dtype):
+    """One long key at position 3 among 900 ordinary ones, over fourteen pages: every later row must find it (without a
+    window, or as one of the kept first tokens) whether it comes in the prompt, in a later portion or token by token."""
+    d, T = 32, 900
+    params = dict(hidden_size=d, heads=2, kv_heads=1, dim=d // 2, vdim=d // 2, conv=None, qk_norm_eps=None, rot_dims=0,
+                  scale=1.0, window=window, keep_first=keep_first)
+    eye = torch.eye(d).to(torch.bfloat16)
+    weights = {"m.q": eye, "m.k": eye[:d // 2], "m.v": eye[d // 2:], "m.o": eye}
+    g = torch.Generator().manual_seed(11)
+    h = 0.1 * torch.randn(T, d, generator=g)
+    h[:, 0] = 1.0
+    h[:, d // 2] = 1.0                                       # both query heads look along the first key axis
+    h[3, 0] = 20.0
+    h[3, d // 2:] = 7.0                                      # the far token's value
+    h = h.to(torch.bfloat16).double()
+    hs = Harness("window_attention", params, dtype, weights=weights, capacity=1024)
+    for portions in ([{"a": T}], [{"a": 500}, {"a": 300}] + [{"a": 1}] * 100, [{"a": 2}] * 450):
+        got = hs.run({"a": h}, portions)["a"]
+        assert float((got[10:] - 7.0).abs().max()) < (1e-3 if dtype == torch.float32 else 0.1), len(portions)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_parallel_pair(dtype):
     left = dict(ATT[0])
     right = dict(LRU[0], hidden_size=48)

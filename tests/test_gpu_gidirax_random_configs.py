@@ -1,0 +1,90 @@
+"""Gidirax configurations drawn at random (fixed seed): layer orders, head counts and groupings, head sizes that are odd
+multiples of 4 and sizes the tensor-core kernels take, key and value sizes equal or not, 1 to 4 taps or none, windows from 1
+to 300 with and without kept first tokens or no window, partial rotation, gate blocks, expert counts with and without
+groups, ranks, layers without a feed-forward; both dtypes.  Each is run whole, with its tail decoded and in a batch of two
+with unequal lengths, against the plain implementation."""
+import json
+import random
+
+import pytest
+import torch
+
+import citlali_b200 as cb
+import plain_gidirax as plain
+import replay
+from gidirax_models import delta, make_weights, moe, par, ssm
+from helpers import random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def draw(i):
+    rng = random.Random(4000 + i)
+    width = rng.choice([40, 64, 72, 128])
+
+    def mlp():
+        kind = rng.random()
+        if kind < 0.2:
+            return None
+        experts = rng.choice([2, 4, 6, 8, 12, 16])
+        if kind < 0.5:
+            return moe(experts, rng.randint(1, min(experts, 4)), rng.choice([16, 24, 40, 64]))
+        count = rng.choice([c for c in (1, 2, 3, 4, 6, 8) if experts % c == 0])
+        keep = rng.randint(1, count)
+        top = rng.randint(1, min(4, keep * (experts // count)))
+        return moe(experts, top, rng.choice([16, 24, 40, 64]), count, keep)
+
+    def layer():
+        kind = rng.choice(["mamba2", "parallel", "channel_delta"])
+        if kind == "mamba2":
+            groups = rng.choice([1, 2, 3])
+            heads = groups * rng.randint(1, 3)
+            vdim = rng.choice([8, 12, 20, 32, 48])
+            ng = rng.choice([n for n in (1, 2, 3, 4) if (heads * vdim) % n == 0])
+            return ssm(heads, vdim, rng.choice([8, 16, 40, 64, 100]), groups, ng, rng.choice([None, 2, 3, 4]), mlp())
+        if kind == "channel_delta":
+            kv = rng.randint(1, 3)
+            return delta(kv * rng.randint(1, 2), kv, rng.choice([8, 20, 32, 64, 96]), rng.choice([8, 12, 32, 40]),
+                         rng.choice([None, 1, 2, 3, 4]), mlp(), rng.choice([4, 8, 24]), rng.choice([4, 8, 16]))
+        kv = rng.randint(1, 3)
+        dim = rng.choice([8, 12, 16, 32, 48, 64, 80])
+        vdim = dim if rng.random() < 0.5 else rng.choice([8, 20, 24, 64])
+        window = rng.choice([None, 1, 7, 64, 65, 100, 300])
+        blocks = rng.choice([1, 2, 4])
+        return par(kv * rng.randint(1, 3), kv, dim, vdim, rng.choice([None, 2, 3, 4]), window,
+                   rng.choice([0, 1, 5, 70]) if window is not None else 0,
+                   rng.choice([None, 0, 4, dim]), rng.choice([1e2, 1e4, 1e6]), rng.choice([0.1, 0.2, dim ** -0.5]),
+                   blocks * rng.choice([8, 20, 32]), blocks, rng.choice([None, 2, 4]), mlp(),
+                   rng.choice([0.5, 1.0, 1.4]), rng.choice([0.6, 1.0, 1.2]))
+
+    return {"architecture": "Gidirax", "vocab": rng.choice([130, 256, 500]), "width": width,
+            "norm": {"eps": rng.choice([1e-5, 1e-6])}, "layers": [layer() for _ in range(rng.randint(2, 5))]}
+
+
+@pytest.mark.parametrize("i", range(12))
+def test_random_configuration(i, tmp_path):
+    d = draw(i)
+    cfg = cb.config_from_dict(json.loads(json.dumps(d)))
+    w = make_weights(cfg, 600 + i)
+    path = str(tmp_path / "m")
+    import os
+    os.makedirs(path)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg.to_dict(), f)
+    cb.write_safetensors(os.path.join(path, "model.safetensors"), lambda: iter(w.items()), metadata={"format": "pt"})
+    reqs = [("a", random_tokens(d["vocab"], 150, 3 * i + 1)), ("b", random_tokens(d["vocab"], 47, 3 * i + 2))]
+    want = {rid: plain.forward(cfg.to_dict(), w, toks) for rid, toks in reqs}
+    for dtype, tol, most in (("float32", 3e-5, 1.0), ("bfloat16", 4e-2, 0.75)):
+        s = cb.InferenceSession().load_model(path, max_context=256, dtype=dtype, max_batch=2)
+        for what, steps in (("whole", replay.whole(reqs)), ("tail", replay.tail(reqs, last=40)),
+                            ("batched", replay.batched(reqs, [100, 20], 2))):
+            got = replay.run_in_process(s, steps)
+            good = 0
+            for (rid, pos), row in got.items():
+                ref = want[rid][pos]
+                err = float((row.double() - ref).abs().max())
+                if err <= tol * float(ref.abs().max()):
+                    good += 1
+                else:                     # in bfloat16 a router's close call may fall the other way (see the replay tests)
+                    assert dtype != "float32", f"configuration {i} {what}: {rid} position {pos}: {err:.3e}"
+            assert good >= most * len(got), f"configuration {i} {dtype} {what}: only {good} of {len(got)} positions agree"
