@@ -74,17 +74,22 @@ def test_random_configuration(i, tmp_path):
     cb.write_safetensors(os.path.join(path, "model.safetensors"), lambda: iter(w.items()), metadata={"format": "pt"})
     reqs = [("a", random_tokens(d["vocab"], 150, 3 * i + 1)), ("b", random_tokens(d["vocab"], 47, 3 * i + 2))]
     want = {rid: plain.forward(cfg.to_dict(), w, toks) for rid, toks in reqs}
-    for dtype, tol, most in (("float32", 3e-5, 1.0), ("bfloat16", 4e-2, 0.75)):
+    # 32-bit: every position within rounding of the exact evaluation.  bfloat16: a router's close call may fall the other
+    # way, and every position behind it in the sequence then differs (several routed layers make that likelier): most
+    # positions must agree and the median error must be small; each bfloat16 kernel is held strictly where it is tested alone
+    for dtype, tol, most in (("float32", 3e-5, 1.0), ("bfloat16", 4e-2, 0.6)):
         s = cb.InferenceSession().load_model(path, max_context=256, dtype=dtype, max_batch=2)
         for what, steps in (("whole", replay.whole(reqs)), ("tail", replay.tail(reqs, last=40)),
                             ("batched", replay.batched(reqs, [100, 20], 2))):
             got = replay.run_in_process(s, steps)
-            good = 0
+            good, errs = 0, []
             for (rid, pos), row in got.items():
                 ref = want[rid][pos]
                 err = float((row.double() - ref).abs().max())
+                errs.append(err / float(ref.abs().max()))
                 if err <= tol * float(ref.abs().max()):
                     good += 1
                 else:                     # in bfloat16 a router's close call may fall the other way (see the replay tests)
                     assert dtype != "float32", f"configuration {i} {what}: {rid} position {pos}: {err:.3e}"
             assert good >= most * len(got), f"configuration {i} {dtype} {what}: only {good} of {len(got)} positions agree"
+            assert sorted(errs)[len(errs) // 2] <= tol / 2, f"configuration {i} {dtype} {what}: median error {sorted(errs)[len(errs) // 2]:.3e}"
