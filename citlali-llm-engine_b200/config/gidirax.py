@@ -46,7 +46,8 @@ def _check_attention(m, where):
     kv = _int(m, "kv_heads", where) if m.get("kv_heads") is not None else heads
     require(heads % kv == 0, f"config.json: {where}.heads {heads} is not a multiple of kv_heads {kv}")
     dim = _int(m, "dim", where)
-    _int(m, "vdim", where)
+    if m.get("vdim") is not None:                 # absent: values have the keys' size
+        _int(m, "vdim", where)
     _number(m, "scale", where)
     _optional_conv(m, where)
     if m.get("mask") is not None:
@@ -179,7 +180,7 @@ class GidiraxConfig:
         mask, rot = l.get("mask"), l.get("rot")
         left = {"kind": "window_attention", "prefix": lp, "params": {
             "hidden_size": self.width, "heads": l["heads"], "kv_heads": l.get("kv_heads") or l["heads"], "dim": l["dim"],
-            "vdim": l["vdim"], "conv": l.get("conv"), "qk_norm_eps": eps, "scale": l["scale"],
+            "vdim": l.get("vdim") or l["dim"], "conv": l.get("conv"), "qk_norm_eps": eps, "scale": l["scale"],
             "rot_dims": rot["dims"] if rot is not None else 0, "rot_base": rot["base"] if rot is not None else 1.0,
             "window": mask["size"] if mask is not None else None,
             "keep_first": (mask.get("keep_first") or 0) if mask is not None else 0,

@@ -70,7 +70,8 @@ def ssm_scan(x, B, C, dt, a, D):
 
 def mamba2_mixer(h, w, p, m, eps):
     T = h.shape[0]
-    H, P, N, G, NG = m["heads"], m["vdim"], m["state"], m["groups"], m["norm_groups"]
+    H, P, N = m["heads"], m["vdim"], m["state"]
+    G, NG = m.get("groups") or 1, m.get("norm_groups") or 1
     inner = H * P
     proj = h @ f64(w[p + ".in"]).T
     z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N:]
@@ -119,7 +120,8 @@ def visible(T, size, keep_first):
 
 def window_attention_mixer(h, w, p, m, eps):
     T = h.shape[0]
-    H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, D = m["heads"], m["dim"]
+    G, V = m.get("kv_heads") or H, m.get("vdim") or D
     def branch(name, heads, size):
         x = h @ f64(w[f"{p}.{name}"]).T
         if m.get("conv") is not None:
